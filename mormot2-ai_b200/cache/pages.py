@@ -66,22 +66,23 @@ class GroupPlan:
     n_pages: int
     max_pages: int      # entries of a sequence's page-table row
     ring_pages: int
+    planes: int = 2     # 2: keys and values; 1: one row per token (a latent)
 
 
 def plan_groups(needs: Dict[int, Tuple[int, int, int]], max_tokens: int, max_context: int,
                 max_slots: int, chunk: int) -> List[GroupPlan]:
-    """Groups the lines by (kv_heads, head_dim, window) and sizes each group's pool.
+    """Groups the lines by (kv_heads, head_dim, window, planes) and sizes each group's pool.
 
-    ``needs[line] = (kv_heads, head_dim, window)``; ``max_tokens`` is the most tokens that live
+    ``needs[line] = (kv_heads, head_dim, window)`` or ``(kv_heads, head_dim, window, planes)``; ``max_tokens`` is the most tokens that live
     sequences hold together (each rounded up to whole pages); ``chunk`` is the most new
     positions of one sequence in one pass of the model.
     """
     total_pages = pages_for(max_tokens)
-    groups: Dict[Tuple[int, int, int], GroupPlan] = {}
+    groups: Dict[Tuple[int, ...], GroupPlan] = {}
     for line in sorted(needs):
-        key = needs[line]
+        key = tuple(needs[line]) + (2,) * (4 - len(needs[line]))
         if key not in groups:
-            kvh, hd, window = key
+            kvh, hd, window, planes = key
             full = pages_for(max_context)
             ring = 0
             if window > 0:
@@ -92,7 +93,7 @@ def plan_groups(needs: Dict[int, Tuple[int, int, int]], max_tokens: int, max_con
                     ring = span
             per_seq = ring if ring else full
             groups[key] = GroupPlan(kvh, hd, window, [], min(total_pages, max_slots * per_seq),
-                                    per_seq, ring)
+                                    per_seq, ring, planes)
         groups[key].lines.append(line)
     return list(groups.values())
 

@@ -22,7 +22,7 @@ from .pages import PAGE, CacheBook, GroupPlan
 class CacheLine:
     """What a mixer gets of its line: pools, the page table of its group and the ring size."""
     k: torch.Tensor            # [pages, kv_heads, PAGE, head_dim]
-    v: torch.Tensor
+    v: Optional[torch.Tensor]  # None in a group of one plane (rows that hold a latent)
     page_table: torch.Tensor   # int32 [slots, max_pages] on the device
     max_pages: int
     ring_pages: int
@@ -42,7 +42,8 @@ class CacheStorage:
         self.lines: Dict[int, CacheLine] = {}
         for g, plan in enumerate(plans):
             pool = alloc(guards, f"keys and values of group {g}",
-                         (len(plan.lines), 2, plan.n_pages, plan.kv_heads, PAGE, plan.head_dim),
+                         (len(plan.lines), plan.planes, plan.n_pages, plan.kv_heads, PAGE,
+                          plan.head_dim),
                          dtype, device)
             table = alloc(guards, f"page table of group {g}", (max_slots, plan.max_pages),
                           torch.int32, device)
@@ -53,7 +54,8 @@ class CacheStorage:
             self.tables.append(table)
             self.tables_host.append(host)
             for i, line in enumerate(plan.lines):
-                self.lines[line] = CacheLine(pool[i, 0], pool[i, 1], table, plan.max_pages,
+                self.lines[line] = CacheLine(pool[i, 0], pool[i, 1] if plan.planes > 1 else None,
+                                             table, plan.max_pages,
                                              plan.ring_pages, plan.window, plan.kv_heads,
                                              plan.head_dim)
         # fixed-size state per slot, at its initial value when a sequence starts; beside it a

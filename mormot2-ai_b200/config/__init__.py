@@ -1,10 +1,12 @@
 """Typed configurations, the model as data (``ModelSpec``) and the architecture registry."""
 from .spec import LayerSpec, ModelSpec, PartSpec, Run
 from .qwen3 import Qwen3Config
+from .busavik import BusavikConfig
 from .registry import (architectures, config_of_folder, family_of, read_config_json,
                        register_architecture)
 
 register_architecture(Qwen3Config, Qwen3Config.ARCHITECTURE, Qwen3Config.MODEL_TYPE)
+register_architecture(BusavikConfig, BusavikConfig.ARCHITECTURE, BusavikConfig.MODEL_TYPE)
 
-__all__ = ["LayerSpec", "ModelSpec", "PartSpec", "Run", "Qwen3Config", "architectures",
+__all__ = ["LayerSpec", "ModelSpec", "PartSpec", "Run", "Qwen3Config", "BusavikConfig", "architectures",
            "config_of_folder", "family_of", "read_config_json", "register_architecture"]

@@ -1,7 +1,8 @@
 """One registry from an architecture's name to its model family.
 
 A family is a configuration class with ``from_dict(doc, source)``, ``to_dict()`` and
-``to_model_spec()``. The name looked up is ``architectures[0]`` of config.json, else its
+``to_model_spec()``. The name looked up is ``architectures[0]`` of config.json (or its
+``architecture``, where a design writes one name instead of a list), else its
 ``model_type`` (the reference registers classes by ``model_type`` and the first registered
 wins: ``decoder.pas:3434-3456``; it names the unknown value in its error, ``:3480-3482``).
 """
@@ -33,6 +34,8 @@ def family_of(doc: Dict[str, Any], source: str = "config") -> Any:
     if not isinstance(doc, dict):
         raise ConfigError(f"{source} is no JSON object")
     names = doc.get("architectures")
+    if names is None and isinstance(doc.get("architecture"), str):
+        names = [doc["architecture"]]
     if isinstance(names, list) and names:
         if names[0] in _BY_ARCHITECTURE:
             return _BY_ARCHITECTURE[names[0]]

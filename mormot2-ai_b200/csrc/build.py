@@ -47,6 +47,8 @@ SOURCES = {
     "gemm_tc": "gemm_tc.cu",
     "attention_mma": "attention_mma.cu",
     "attention_tc": "attention_tc.cu",
+    "latent": "latent.cu",
+    "moe": "moe.cu",
 }
 HEADERS = ["common.cuh"]
 EXTRA_HEADERS = {"gemm_tc": ["tc_common.cuh"],

@@ -295,3 +295,115 @@ MB_EXPORT int mb_advance_decode(int* tok_ids, int* tok_pos, const int* chosen, i
                                                                           chosen, history, B);
   MB_CHECK_LAUNCH("mb_advance_decode");
 }
+
+// ------------------------------------------------------------------ Dynamic Tanh
+// y[r, c] = tanh(alpha * x[src, c]) * w[c] + b[c], value by value in float32: a norm without a
+// mean or a variance. alpha is one float32 on the device. As with RMSNorm, `parts` partial
+// products [parts][T][H] are first added into the residual row in place, in split order.
+template <typename TW, typename TO>
+__global__ void dynamic_tanh_kernel(float* __restrict__ x, const float* __restrict__ partial,
+                                    int parts, size_t part_stride, const TW* __restrict__ w,
+                                    const TW* __restrict__ b, const float* __restrict__ alpha,
+                                    TO* __restrict__ y, const int* __restrict__ rows, int H) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* xr = x + (size_t)src * H;
+  const float a = alpha[0];
+  TO* yr = y + (size_t)r * H;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float v = xr[c];
+    if (parts > 0) {
+      for (int p = 0; p < parts; ++p) v += partial[p * part_stride + (size_t)src * H + c];
+      xr[c] = v;
+    }
+    yr[c] = from_f32<TO>(fmaf(tanhf(a * v), to_f32<TW>(w[c]), to_f32<TW>(b[c])));
+  }
+}
+
+MB_EXPORT int mb_dynamic_tanh(float* x, const float* partial, int parts, long long part_stride,
+                              const void* w, const void* b, int w_dtype, const float* alpha,
+                              void* y, int y_dtype, const int* rows, int R, int H, void* stream) {
+  if (R <= 0) return 0;
+  if (parts > 0 && rows) MB_FAIL("mb_dynamic_tanh: partial sums with a row gather");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+#define GO(TW_, TO_)                                                                          \
+  mb_launch(dynamic_tanh_kernel<TW_, TO_>, dim3(R), dim3(threads), 0, s, x, partial, parts,   \
+            (size_t)part_stride, (const TW_*)w, (const TW_*)b, alpha, (TO_*)y, rows, H)
+  if (w_dtype == MB_F32 && y_dtype == MB_F32) GO(float, float);
+  else if (w_dtype == MB_F32) GO(float, __nv_bfloat16);
+  else if (y_dtype == MB_F32) GO(__nv_bfloat16, float);
+  else GO(__nv_bfloat16, __nv_bfloat16);
+#undef GO
+  MB_CHECK_LAUNCH("mb_dynamic_tanh");
+}
+
+// ------------------------------------------------------------------ gated activation
+// in [T, 2I]: gate in columns [0, I), up in [I, 2I); out[t, c] = act(g + bg[c]) * (u + bu[c])
+// with act = SiLU (0) or the tanh form of GELU (1): 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+// The biases may be null. When `x` is given, the block that handles the first columns of a row
+// also adds `xb` [H] into the float32 residual row x[t, :]: the bias of the product that follows
+// and accumulates onto that row.
+enum { ACT_SILU = 0, ACT_GELU_TANH = 1 };
+__device__ __forceinline__ float act_of(float z, int act) {
+  if (act == ACT_GELU_TANH)
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z / (1.0f + expf(-z));
+}
+
+template <typename T, typename TW>
+__global__ void gated_act_kernel(const T* __restrict__ in, T* __restrict__ out, int I, int act,
+                                 const TW* __restrict__ bg, const TW* __restrict__ bu,
+                                 float* __restrict__ x, const TW* __restrict__ xb, int H) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  const int t = blockIdx.y;
+  const T* row = in + (size_t)t * 2 * I;
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < I; c += gridDim.x * blockDim.x) {
+    float g = to_f32<T>(row[c]), u = to_f32<T>(row[I + c]);
+    if (bg) g += to_f32<TW>(bg[c]);
+    if (bu) u += to_f32<TW>(bu[c]);
+    out[(size_t)t * I + c] = from_f32<T>(act_of(g, act) * u);
+  }
+  if (x && blockIdx.x == 0)
+    for (int c = threadIdx.x; c < H; c += blockDim.x) x[(size_t)t * H + c] += to_f32<TW>(xb[c]);
+}
+
+MB_EXPORT int mb_gated_act(const void* in, void* out, int dtype, int T, int I, int act,
+                           const void* bg, const void* bu, int b_dtype, float* x, const void* xb,
+                           int H, void* stream) {
+  if (T <= 0) return 0;
+  if (act != ACT_SILU && act != ACT_GELU_TANH) MB_FAIL("mb_gated_act: activation %d", act);
+  if ((x == nullptr) != (xb == nullptr)) MB_FAIL("mb_gated_act: x and its bias come together");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = 256;
+  dim3 grid(max(1, min((I + threads - 1) / threads, 64)), T);
+#define GO(T_, TW_)                                                                          \
+  mb_launch(gated_act_kernel<T_, TW_>, grid, dim3(threads), 0, s, (const T_*)in, (T_*)out, I, \
+            act, (const TW_*)bg, (const TW_*)bu, x, (const TW_*)xb, H)
+  if (dtype == MB_F32) {
+    if (b_dtype == MB_F32) GO(float, float); else GO(float, __nv_bfloat16);
+  } else {
+    if (b_dtype == MB_F32) GO(__nv_bfloat16, float); else GO(__nv_bfloat16, __nv_bfloat16);
+  }
+#undef GO
+  MB_CHECK_LAUNCH("mb_gated_act");
+}
+
+// ------------------------------------------------------------------ a constant factor
+__global__ void scale_kernel(float* __restrict__ x, size_t total, float s) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x)
+    x[i] *= s;
+}
+
+MB_EXPORT int mb_scale(float* x, long long total, float factor, void* stream) {
+  if (total <= 0) return 0;
+  const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  mb_launch(scale_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, (size_t)total, factor);
+  MB_CHECK_LAUNCH("mb_scale");
+}

@@ -1,0 +1,287 @@
+// A feed-forward of routed experts on the device, without a round trip to the host: the
+// router's choice, the lists of tokens per expert, the experts' two products over those lists
+// and the weighted sum into the residual. float32 arithmetic on the CUDA cores for float32
+// and bfloat16 storage.
+//
+//   moe_route    per token: the `top` largest router logits (the lower index on a tie), their
+//                weights = softmax over the chosen logits only, and the shared expert's gate
+//                sigmoid(logit) when the router's product carries that column
+//   moe_plan     assignments (token, k) listed expert by expert, cut into tiles of rows
+//   moe_gemm     for every tile the product with its expert's weight:
+//                up:   act[r, :] = f(h[token(r)] · Wgᵀ) * (h[token(r)] · Wuᵀ)   (rows gathered)
+//                down: y[a(r), :] = weight[a(r)] * (act[r] · Wdᵀ)              (float32, scattered
+//                      to the assignment's own row, so the sum below has a fixed order)
+//   moe_combine  x[t] += sum_k y[t·top + k] + gate[t] · shared[t]
+//
+// The order of an expert's rows in its list comes from atomic counters and may differ from run
+// to run; no result depends on it (a row's sums are formed alone, in a fixed order).
+#include "common.cuh"
+
+MB_DEFINE_LAST_ERROR
+
+// ------------------------------------------------------------------ route
+// z [T, ldz] float32: columns [0, E) the experts' logits, column shared_col (or -1) the shared
+// expert's gate logit. One warp per token.
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ z, int ldz, int E, int top, int shared_col,
+                 int* __restrict__ ids, float* __restrict__ w, float* __restrict__ sg, int T) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const float* zr = z + (size_t)t * ldz;
+  float last_v = INFINITY;
+  int last_i = -1;
+  float first = 0.f, sum = 0.f, mine = 0.f;  // lane k keeps the k-th chosen logit
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int i = lane; i < E; i += 32) {
+      const float v = zr[i];
+      const bool open = v < last_v || (v == last_v && i > last_i);
+      if (open && (v > best || (v == best && i < best_i))) {
+        best = v;
+        best_i = i;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ov > best || (ov == best && oi < best_i)) {
+        best = ov;
+        best_i = oi;
+      }
+    }
+    if (best_i == 0x7fffffff) {  // nothing left that compares (NaNs): take the next index
+      best_i = min(E - 1, last_i + 1);
+      best = zr[best_i];
+    }
+    if (k == 0) first = best;
+    const float e = expf(best - first);
+    sum += e;
+    if (lane == k) mine = e;
+    if (lane == 0) ids[(size_t)t * top + k] = best_i;
+    last_v = best;
+    last_i = best_i;
+  }
+  if (lane < top) w[(size_t)t * top + lane] = mine / sum;
+  if (sg && lane == 0) sg[t] = 1.0f / (1.0f + expf(-zr[shared_col]));
+}
+
+MB_EXPORT int mb_moe_route(const float* z, int ldz, int E, int top, int shared_col, int* ids,
+                           float* w, float* sg, int T, void* stream) {
+  if (T <= 0) return 0;
+  if (top <= 0 || top > 32 || top > E) MB_FAIL("mb_moe_route: %d of %d experts", top, E);
+  if ((sg != nullptr) != (shared_col >= 0)) MB_FAIL("mb_moe_route: the shared gate and its column");
+  mb_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, (cudaStream_t)stream, z, ldz, E,
+            top, shared_col, ids, w, sg, T);
+  MB_CHECK_LAUNCH("mb_moe_route");
+}
+
+// ------------------------------------------------------------------ plan
+// plan (int32): [0] number of tiles, [1 .. 1+E] first list row of every expert (E + 1 values),
+// then perm[A] (the assignment a = t·top + k at every list row), then tile_expert[max_tiles]
+// and tile_row0[max_tiles]. One block.
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ ids, int A, int E, int bm, int max_tiles,
+                int* __restrict__ plan) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  extern __shared__ int counts[];  // E counters, then E cursors
+  int* cursor = counts + E;
+  int* offsets = plan + 1;
+  int* perm = offsets + E + 1;
+  int* tile_e = perm + A;
+  int* tile_r0 = tile_e + max_tiles;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int a = threadIdx.x; a < A; a += blockDim.x) {
+    const int e = ids[a];
+    if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      offsets[e] = at;
+      cursor[e] = at;
+      for (int r0 = 0; r0 < counts[e] && tiles < max_tiles; r0 += bm) {
+        tile_e[tiles] = e;
+        tile_r0[tiles] = at + r0;
+        ++tiles;
+      }
+      at += counts[e];
+    }
+    offsets[E] = at;
+    plan[0] = tiles;
+  }
+  __syncthreads();
+  for (int a = threadIdx.x; a < A; a += blockDim.x) {
+    const int e = ids[a];
+    if (e >= 0 && e < E) perm[atomicAdd(&cursor[e], 1)] = a;
+  }
+}
+
+MB_EXPORT int mb_moe_plan(const int* ids, int A, int E, int bm, int max_tiles, int* plan,
+                          void* stream) {
+  if (A <= 0) return 0;
+  if (E > 4096) MB_FAIL("mb_moe_plan: %d experts", E);
+  if (max_tiles < (A + bm - 1) / bm + E) MB_FAIL("mb_moe_plan: room for %d tiles", max_tiles);
+  mb_launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int),
+            (cudaStream_t)stream, ids, A, E, bm, max_tiles, plan);
+  MB_CHECK_LAUNCH("mb_moe_plan");
+}
+
+// ------------------------------------------------------------------ the experts' products
+__device__ __forceinline__ float moe_act(float z, int act) {
+  if (act == 1)
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z / (1.0f + expf(-z));
+}
+
+#define MG_BN 64
+#define MG_BK 16
+// UP:   in = h [T, K] (row of list row r: perm[r] / top), W [E][2N][K] (gate rows, then up
+//       rows), out = act [A, N] at list row r.
+// DOWN: in = act [A, K] at list row r, W [E][N][K], out = y [A, N] float32 at row perm[r],
+//       multiplied by weight[perm[r]].
+template <typename T, typename TW, int BM, bool UP>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const T* __restrict__ in, const TW* __restrict__ W, void* __restrict__ out,
+                const int* __restrict__ plan, int A, int E, int max_tiles, int top, int N, int K,
+                int act, const float* __restrict__ weight) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  constexpr int NW = UP ? 2 : 1;
+  constexpr int TM = BM / 16;
+  const int tile = blockIdx.y;
+  if (tile >= plan[0]) return;
+  const int* offsets = plan + 1;
+  const int* perm = offsets + E + 1;
+  const int e = perm[A + tile];
+  const int r0 = perm[A + max_tiles + tile];
+  const int rows = min(BM, offsets[e + 1] - r0);
+  __shared__ float As[MG_BK][BM + 4];
+  __shared__ float Ws[NW][MG_BK][MG_BN + 4];
+  __shared__ int src[BM];
+  const int tid = threadIdx.x;
+  if (tid < BM) src[tid] = tid < rows ? perm[r0 + tid] : -1;
+  __syncthreads();
+  const int n0 = blockIdx.x * MG_BN;
+  const TW* We = W + (size_t)e * NW * N * K;
+  const int tr = (tid / 16) * TM, tc = (tid % 16) * 4;
+  float acc[NW][TM][4];
+#pragma unroll
+  for (int w = 0; w < NW; ++w)
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[w][i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += MG_BK) {
+    for (int el = tid; el < BM * MG_BK; el += 256) {
+      const int r = el / MG_BK, c = el % MG_BK;
+      const int gk = k0 + c;
+      float v = 0.f;
+      if (r < rows && gk < K) {
+        const size_t row = UP ? (size_t)(src[r] / top) : (size_t)(r0 + r);
+        v = to_f32<T>(in[row * K + gk]);
+      }
+      As[c][r] = v;
+    }
+    for (int el = tid; el < MG_BN * MG_BK; el += 256) {
+      const int r = el / MG_BK, c = el % MG_BK;
+      const int gn = n0 + r, gk = k0 + c;
+#pragma unroll
+      for (int w = 0; w < NW; ++w)
+        Ws[w][c][r] = (gn < N && gk < K) ? to_f32<TW>(We[((size_t)w * N + gn) * K + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < MG_BK; ++k) {
+      float a[TM];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) a[i] = As[k][tr + i];
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        float b[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b[j] = Ws[w][k][tc + j];
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[w][i][j] = fmaf(a[i], b[j], acc[w][i][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int r = tr + i;
+    if (r >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tc + j;
+      if (gn >= N) continue;
+      if (UP) {
+        ((T*)out)[(size_t)(r0 + r) * N + gn] =
+            from_f32<T>(moe_act(acc[0][i][j], act) * acc[NW - 1][i][j]);
+      } else {
+        const int a = src[r];
+        ((float*)out)[(size_t)a * N + gn] = weight[a] * acc[0][i][j];
+      }
+    }
+  }
+}
+
+MB_EXPORT int mb_moe_gemm(const void* in, int dtype, const void* W, int w_dtype, void* out,
+                          const int* plan, int A, int E, int max_tiles, int bm, int top, int N,
+                          int K, int up, int act, const float* weight, void* stream) {
+  if (A <= 0) return 0;
+  if (bm != 16 && bm != 64) MB_FAIL("mb_moe_gemm: tiles of %d rows", bm);
+  if (!up && weight == nullptr) MB_FAIL("mb_moe_gemm: the second product needs the weights");
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid((N + MG_BN - 1) / MG_BN, max_tiles);
+#define GO(T_, TW_, BM_, UP_)                                                                \
+  mb_launch(moe_gemm_kernel<T_, TW_, BM_, UP_>, grid, dim3(256), 0, s, (const T_*)in,        \
+            (const TW_*)W, out, plan, A, E, max_tiles, top, N, K, act, weight)
+#define GO3(T_, TW_)                                                  \
+  {                                                                   \
+    if (bm == 16) { if (up) GO(T_, TW_, 16, true); else GO(T_, TW_, 16, false); } \
+    else { if (up) GO(T_, TW_, 64, true); else GO(T_, TW_, 64, false); }          \
+  }
+  if (dtype == MB_F32) {
+    if (w_dtype == MB_F32) GO3(float, float) else GO3(float, __nv_bfloat16)
+  } else {
+    if (w_dtype == MB_F32) GO3(__nv_bfloat16, float) else GO3(__nv_bfloat16, __nv_bfloat16)
+  }
+#undef GO3
+#undef GO
+  MB_CHECK_LAUNCH("mb_moe_gemm");
+}
+
+// ------------------------------------------------------------------ combine
+// x[t, c] += sum_k y[(t·top + k), c] (k ascending) + sg[t] · shared[t, c]
+__global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ y, int top,
+                                   const float* __restrict__ shared, const float* __restrict__ sg,
+                                   int H) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  const int t = blockIdx.x;
+  const float g = sg ? sg[t] : 1.0f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float v = 0.f;
+    for (int k = 0; k < top; ++k) v += y[((size_t)t * top + k) * H + c];
+    if (shared) v = fmaf(g, shared[(size_t)t * H + c], v);
+    x[(size_t)t * H + c] += v;
+  }
+}
+
+MB_EXPORT int mb_moe_combine(float* x, const float* y, int top, const float* shared,
+                             const float* sg, int T, int H, void* stream) {
+  if (T <= 0) return 0;
+  mb_launch(moe_combine_kernel, dim3(T), dim3(H >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, x,
+            y, top, shared, sg, H);
+  MB_CHECK_LAUNCH("mb_moe_combine");
+}

@@ -73,9 +73,9 @@ class Engine:
         self.max_slots = max_slots or max(1, min(max_tokens // PAGE, 1024))
         self.prefill_chunk = max(1, prefill_chunk)
         self.max_step_tokens = max(max_step_tokens, self.max_slots)
-        build.compile_libraries(rt.libraries())
+        build.compile_libraries(rt.libraries(self.model.parts()))
         self.model.bind(weights, rt)
-        needs = {line: (n.kv_heads, n.head_dim, n.window)
+        needs = {line: (n.kv_heads, n.head_dim, n.window, n.planes)
                  for line, n in self.model.line_needs.items()}
         self.plans = plan_groups(needs, max_tokens, self.max_context, self.max_slots,
                                  self.prefill_chunk)

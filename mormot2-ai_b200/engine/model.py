@@ -94,7 +94,8 @@ class DecoderModel:
                     raise ConfigError(f"entry {i} of the order reads cache line {line} "
                                       "before any entry wrote it")
                 have = self.line_needs[line]
-                if (have.kv_heads, have.head_dim) != (need.kv_heads, need.head_dim):
+                if ((have.kv_heads, have.head_dim, have.planes)
+                        != (need.kv_heads, need.head_dim, need.planes)):
                     raise ConfigError(f"entry {i} of the order reads cache line {line} with "
                                       "other head sizes than it was written with")
 

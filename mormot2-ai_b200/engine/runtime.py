@@ -106,12 +106,29 @@ class Runtime:
         self._raise_if(got[0])
         return got[1:]
 
-    def libraries(self):
-        """The kernel libraries that a model of this runtime needs."""
-        libs = ["elementwise", "rope", "gemm_simt", "attention_simt", "sampling"]
+    def libraries(self, parts=None):
+        """The kernel libraries that a model of this runtime needs: those of every model and
+        what its ``parts`` name (``Part.libraries``); without ``parts``, all of the built-in
+        attention's."""
+        libs = ["elementwise", "gemm_simt"]
         if self.fast_kernels:
-            libs += ["gemm_tc", "attention_mma", "attention_tc"]
+            libs.append("gemm_tc")
+        if parts is None:
+            return libs + ["sampling"] + self.attention_libraries()
+        for part in parts:
+            for name in part.libraries(self):
+                if name not in libs:
+                    libs.append(name)
         return libs
+
+    def attention_libraries(self):
+        libs = ["rope", "attention_simt"]
+        if self.fast_kernels:
+            libs += ["attention_mma", "attention_tc"]
+        return libs
+
+    def latent_attention(self, q, out, step, line, nh, kv_rank, rot_dim, window, scale) -> None:
+        K.latent_attention(q, out, step, line, nh, kv_rank, rot_dim, window, scale)
 
     def attention(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale) -> None:
         if self.fast_kernels:

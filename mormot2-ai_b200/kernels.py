@@ -67,7 +67,11 @@ CLASS_OF = {"mb_gemm_tc": "products", "mb_gemm_simt": "products",
             "mb_attention_prefill_tc": "attention", "mb_rmsnorm": "norms",
             "mb_qk_norm_rope_store": "rotary", "mb_embed": "embedding", "mb_swiglu": "activation",
             "mb_argmax": "sampling", "mb_sample": "sampling", "mb_sample_filtered": "sampling",
-            "mb_advance_decode": "sampling"}
+            "mb_advance_decode": "sampling", "mb_dynamic_tanh": "norms",
+            "mb_gated_act": "activation", "mb_scale": "activation", "mb_latent_prep": "rotary",
+            "mb_heads_gemm": "products", "mb_latent_attention": "attention",
+            "mb_moe_route": "routing", "mb_moe_plan": "routing", "mb_moe_gemm": "products",
+            "mb_moe_combine": "routing"}
 
 
 class Timing:
@@ -241,6 +245,168 @@ def qk_norm_rope_store(qkv, q_norm, k_norm, eps, inv_freq, rot_dim, step, line, 
           _ptr(inv_freq), rot_dim, _ptr(step.tok_slot), _ptr(step.tok_pos),
           _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(line.k), _ptr(line.v),
           T, nh, nkv, hd, 1 if write_kv else 0, _stream())
+
+
+ACT_SILU, ACT_GELU_TANH = 0, 1
+ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
+
+
+def dynamic_tanh(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, alpha: torch.Tensor,
+                 out: torch.Tensor, rows: Optional[torch.Tensor] = None,
+                 n_rows: Optional[int] = None, partial: Optional[torch.Tensor] = None) -> None:
+    """out[r] = tanh(alpha * x[rows[r] or r]) * w + b; ``alpha``: one float32 on the device.
+    ``partial`` [parts, T, H] float32 is first added into x."""
+    H = x.shape[-1]
+    R = n_rows if n_rows is not None else (rows.numel() if rows is not None else x.shape[0])
+    assert x.dtype == torch.float32 and w.numel() == H and b.numel() == H
+    assert alpha.dtype == torch.float32 and w.dtype == b.dtype
+    _contig(x, "x")
+    parts, stride = 0, 0
+    if partial is not None:
+        assert partial.dtype == torch.float32 and partial.is_contiguous()
+        parts, stride = partial.shape[0], partial.stride(0)
+    _call("elementwise", "mb_dynamic_tanh",
+          [_vp, _vp, _i, _ll, _vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _vp],
+          _ptr(x), _ptr(partial), parts, stride, _ptr(w), _ptr(b), code_of(w.dtype), _ptr(alpha),
+          _ptr(out), code_of(out.dtype), _ptr(rows), R, H, _stream())
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: int,
+              gate_bias: Optional[torch.Tensor] = None, up_bias: Optional[torch.Tensor] = None,
+              x: Optional[torch.Tensor] = None, x_bias: Optional[torch.Tensor] = None) -> None:
+    """out[T, I] = act(gate_up[:, :I] + gate_bias) * (gate_up[:, I:] + up_bias); with ``x`` and
+    ``x_bias`` the float32 residual rows also receive that bias (the one of the product that
+    is added onto them next)."""
+    T, I = out.shape
+    assert gate_up.shape == (T, 2 * I) and gate_up.dtype == out.dtype
+    _contig(gate_up, "gate_up"), _contig(out, "out")
+    biases = [b for b in (gate_bias, up_bias, x_bias) if b is not None]
+    assert all(b.dtype == biases[0].dtype for b in biases)
+    if x is not None:
+        assert x.dtype == torch.float32 and x.is_contiguous() and x_bias.numel() == x.shape[1]
+    _call("elementwise", "mb_gated_act",
+          [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _vp],
+          _ptr(gate_up), _ptr(out), code_of(out.dtype), T, I, act, _ptr(gate_bias),
+          _ptr(up_bias), code_of(biases[0].dtype) if biases else F32, _ptr(x), _ptr(x_bias),
+          x.shape[1] if x is not None else 0, _stream())
+
+
+def scale_rows(x: torch.Tensor, factor: float) -> None:
+    """x *= factor (float32, contiguous)."""
+    assert x.dtype == torch.float32
+    _contig(x, "x")
+    _call("elementwise", "mb_scale", [_vp, _ll, _f, _vp], _ptr(x), x.numel(), float(factor),
+          _stream())
+
+
+# ------------------------------------------------------------------------------ latent attention
+def latent_prep(f: torch.Tensor, q_col: int, kv_col: int, q_rank: int, kv_rank: int, rot_dim: int,
+                w_q: torch.Tensor, w_kv: torch.Tensor, eps: float,
+                inv_freq: Optional[torch.Tensor], rot_dims: int, amplitude: float, step, line,
+                cq_out: torch.Tensor, write_cache: bool) -> None:
+    """From the rows of ``f`` [T, ld]: the normed query latent into ``cq_out`` [T, q_rank] and
+    the cache row [normed key/value latent ; rotated shared key part] of every token."""
+    T = f.shape[0]
+    assert f.stride(1) == 1 and cq_out.is_contiguous() and cq_out.dtype == f.dtype
+    assert w_q.dtype == w_kv.dtype and line.k.dtype == f.dtype
+    assert line.head_dim == kv_rank + rot_dim and line.kv_heads == 1
+    _call("latent", "mb_latent_prep",
+          [_vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _vp, _i, _f, _vp, _vp, _vp, _i, _i,
+           _vp, _vp, _i, _i, _vp],
+          _ptr(f), code_of(f.dtype), f.stride(0), q_col, kv_col, q_rank, kv_rank, rot_dim,
+          _ptr(w_q), _ptr(w_kv), code_of(w_q.dtype), float(eps), _ptr(inv_freq), rot_dims,
+          float(amplitude), _ptr(step.tok_slot), _ptr(step.tok_pos), _ptr(line.page_table),
+          line.max_pages, line.ring_pages, _ptr(line.k), _ptr(cq_out), T,
+          1 if write_cache else 0, _stream())
+
+
+def heads_gemm(a: torch.Tensor, lda_h: int, b: torch.Tensor, c: torch.Tensor, ldc_h: int,
+               gate: Optional[torch.Tensor] = None, tail: int = 0, rot_dims: int = 0,
+               inv_freq: Optional[torch.Tensor] = None, amplitude: float = 1.0,
+               tok_pos: Optional[torch.Tensor] = None) -> None:
+    """c[t, h*ldc_h + n] = sum_k a[t, h*lda_h + k] * b[h, n, k] for every head h (``b``
+    [heads, N, K]). ``gate`` [T, >= heads*N]: c is multiplied by its sigmoid. ``tail``: that
+    many values of a behind the K multiplied ones are rotated by the token's position
+    (``rot_dims`` of them turn) and stored behind c's N columns."""
+    heads, N, Kd = b.shape
+    M = a.shape[0]
+    assert a.stride(1) == 1 and c.stride(1) == 1 and a.dtype == c.dtype and c.shape[0] == M
+    _contig(b, "the heads' weight")
+    if gate is not None:
+        assert gate.dtype == a.dtype and gate.stride(1) == 1
+    _call("latent", "mb_heads_gemm",
+          [_vp, _i, _i, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _i, _vp, _f, _vp,
+           _vp],
+          _ptr(a), code_of(a.dtype), a.stride(0), lda_h, _ptr(b), code_of(b.dtype), _ptr(c),
+          c.stride(0), ldc_h, M, N, Kd, heads, _ptr(gate),
+          gate.stride(0) if gate is not None else 0, tail, rot_dims, _ptr(inv_freq),
+          float(amplitude), _ptr(tok_pos), _stream())
+
+
+def latent_attention(q: torch.Tensor, out: torch.Tensor, step, line, nh: int, kv_rank: int,
+                     rot_dim: int, window: int, scale: float) -> None:
+    """Causal attention of every head over the cache rows [latent ; shared rotated key part];
+    q [T, nh * (kv_rank + rot_dim)], out [T, nh * kv_rank] (the weighted latents)."""
+    T = out.shape[0]
+    _contig(out, "out"), _contig(q, "q")
+    assert q.dtype == out.dtype == line.k.dtype
+    _call("latent", "mb_latent_attention",
+          [_vp, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp],
+          _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(line.k), code_of(out.dtype),
+          _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(step.tok_slot),
+          _ptr(step.tok_pos), T, nh, kv_rank, rot_dim, window, float(scale), _stream())
+
+
+# ------------------------------------------------------------------------------ routed experts
+def moe_route(z: torch.Tensor, experts: int, top: int, shared_col: int, ids: torch.Tensor,
+              w: torch.Tensor, sg: Optional[torch.Tensor]) -> None:
+    """Per row of z (float32 router logits): the ``top`` largest of the first ``experts``
+    columns into ``ids`` and the softmax over them into ``w``; ``sg`` = sigmoid of column
+    ``shared_col``."""
+    T = z.shape[0]
+    assert z.dtype == torch.float32 and z.stride(1) == 1
+    assert ids.dtype == torch.int32 and w.dtype == torch.float32
+    _call("moe", "mb_moe_route", [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
+          _ptr(z), z.stride(0), experts, top, shared_col if sg is not None else -1, _ptr(ids),
+          _ptr(w), _ptr(sg), T, _stream())
+
+
+def moe_plan(ids: torch.Tensor, experts: int, bm: int, max_tiles: int,
+             plan: torch.Tensor) -> None:
+    assert plan.dtype == torch.int32 and plan.numel() >= 2 + experts + ids.numel() + 2 * max_tiles
+    _call("moe", "mb_moe_plan", [_vp, _i, _i, _i, _i, _vp, _vp],
+          _ptr(ids), ids.numel(), experts, bm, max_tiles, _ptr(plan), _stream())
+
+
+def moe_gemm(src: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: torch.Tensor,
+             assignments: int, max_tiles: int, bm: int, top: int, up: bool, act: int = ACT_SILU,
+             weight: Optional[torch.Tensor] = None) -> None:
+    """One of the experts' two products over the planned tiles. ``up``: w [E, 2N, K] (gate
+    rows, then up rows), rows of ``src`` [T, K] gathered, out [A, N]. Else w [E, N, K], src
+    [A, K], out [A, N] float32 at the assignment's own row, times ``weight`` [A]."""
+    E = w.shape[0]
+    N = w.shape[1] // (2 if up else 1)
+    Kd = w.shape[2]
+    _contig(src, "src"), _contig(out, "out"), _contig(w, "the experts' weight")
+    assert src.shape[1] == Kd and out.shape[1] == N
+    assert out.dtype == (src.dtype if up else torch.float32)
+    _call("moe", "mb_moe_gemm",
+          [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+          _ptr(src), code_of(src.dtype), _ptr(w), code_of(w.dtype), _ptr(out), _ptr(plan),
+          assignments, E, max_tiles, bm, top, N, Kd, 1 if up else 0, act, _ptr(weight),
+          _stream())
+
+
+def moe_combine(x: torch.Tensor, y: torch.Tensor, top: int, shared: Optional[torch.Tensor],
+                sg: Optional[torch.Tensor]) -> None:
+    """x[t] += sum_k y[t*top + k] + sg[t] * shared[t] (all float32)."""
+    T, H = x.shape
+    assert x.dtype == y.dtype == torch.float32 and y.shape == (T * top, H)
+    _contig(x, "x"), _contig(y, "y")
+    if shared is not None:
+        assert shared.dtype == torch.float32 and shared.shape == (T, H) and shared.is_contiguous()
+    _call("moe", "mb_moe_combine", [_vp, _vp, _i, _vp, _vp, _i, _i, _vp],
+          _ptr(x), _ptr(y), top, _ptr(shared), _ptr(sg), T, H, _stream())
 
 
 # ------------------------------------------------------------------------------ products

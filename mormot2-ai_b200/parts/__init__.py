@@ -2,7 +2,8 @@
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS,
                    CacheNeed, Part, StateNeed, TensorNeed, register_block,
                    register_feed_forward, register_mixer, register_norm, register_position)
-from . import attention, block, embedding, feedforward, norm, position  # noqa: F401  (register)
+from . import (attention, block, embedding, feedforward, latent_attention, moe, norm,  # noqa: F401
+               position)
 from .linear import Linear
 
 __all__ = ["BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITIONS",

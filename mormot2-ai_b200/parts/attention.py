@@ -36,6 +36,9 @@ class GqaAttention(Part):
                               "which the model does not define")
         self.qw, self.kvw = self.nh * self.hd, self.nkv * self.hd
 
+    def libraries(self, rt) -> List[str]:
+        return rt.attention_libraries()
+
     def tensors(self) -> List[TensorNeed]:
         n = self.names
         out = [TensorNeed(n["q"], (self.qw, self.hidden)),

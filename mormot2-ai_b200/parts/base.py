@@ -54,10 +54,13 @@ class TensorNeed:
 @dataclass(frozen=True)
 class CacheNeed:
     """Keys and values that a mixer keeps for every token: ``kv_heads`` x ``head_dim`` each;
-    ``window`` > 0: only the last ``window`` positions are ever read."""
+    ``window`` > 0: only the last ``window`` positions are ever read. ``planes``: 2 for keys
+    and values, 1 for a mixer that keeps one row per token and reads keys and values out of
+    it (a latent from which both are formed: ``head_dim`` is then the row's whole size)."""
     kv_heads: int
     head_dim: int
     window: int = 0
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -90,6 +93,11 @@ class Part:
 
     def cache_need(self) -> Optional[CacheNeed]:
         return None
+
+    def libraries(self, rt: Any) -> List[str]:
+        """The kernel libraries (``csrc/build.py: SOURCES``) that this part launches from,
+        beyond those every model uses; they are compiled before the first step."""
+        return []
 
     def state_need(self) -> Optional[StateNeed]:
         return None

@@ -25,6 +25,8 @@ class PreNormResidualBlock(Part):
     def forward(self, x, step, line, state, writes_cache: bool, pending=None):
         h = self._norm("mixer", x, pending)
         pending = self.mixer.forward(h, x, step, line, state, writes_cache)
+        if "feed_forward" not in self.norms:      # a layer without a feed-forward
+            return pending
         h = self._norm("feed_forward", x, pending)
         return self.feed_forward.forward(h, x, step)
 

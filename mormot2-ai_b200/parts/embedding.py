@@ -1,6 +1,7 @@
 """Token embedding (rows of the table into the float32 residual, no scaling:
 ``decoder.pas:3292-3309`` of the reference) and the head (logits = h · Headᵀ in float32, the
-head being the embedding when tied: ``model.qwen3.pas:555-579``)."""
+head being the embedding when tied: ``model.qwen3.pas:555-579``; a head with ``scale``
+multiplies its float32 logits by that constant)."""
 from __future__ import annotations
 
 from typing import Dict, List
@@ -40,6 +41,7 @@ class LmHead(Part):
         self.name = p["tied_to"] if self.tied else p["name"]
         self.stored_name = p["name"]
         self.vocab, self.hidden = int(p["vocab_size"]), int(p["hidden_size"])
+        self.scale = float(p.get("scale", 1.0))
 
     def tensors(self) -> List[TensorNeed]:
         if self.tied:
@@ -52,7 +54,10 @@ class LmHead(Part):
         self.linear = Linear(weights[self.name], rt)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return self.linear(h, out_dtype=torch.float32)
+        logits = self.linear(h, out_dtype=torch.float32)
+        if self.scale != 1.0:
+            K.scale_rows(logits, self.scale)
+        return logits
 
 
 EMBEDDINGS.register("token_embedding", TokenEmbedding)

@@ -1,5 +1,8 @@
 """RMSNorm: y = w · x / sqrt(mean(x²) + eps), the weight multiplying as it is (not 1 + w);
-sums in float32 (``backend.cpu.pas:1769-1795``, ``ops.cu:116-130`` of the reference)."""
+sums in float32 (``backend.cpu.pas:1769-1795``, ``ops.cu:116-130`` of the reference).
+
+Dynamic Tanh: y = tanh(alpha · x) · w + b with a learned scalar alpha: a norm that forms no
+mean and no variance, value by value in float32."""
 from __future__ import annotations
 
 from typing import Dict, List, Optional
@@ -40,4 +43,36 @@ class RmsNorm(Part):
         return out
 
 
+class DynamicTanh(Part):
+    """``name`` is the weight; the scalar and the shift are stored beside it as
+    ``<name>.alpha`` and ``<name>.b``."""
+    capturable = True
+    accepts_pending = True
+
+    def __init__(self, spec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        self.size = int(spec.params["size"])
+        self.name = prefix + spec.params["name"]
+
+    def tensors(self) -> List[TensorNeed]:
+        return [TensorNeed(self.name, (self.size,), "vector"),
+                TensorNeed(self.name + ".b", (self.size,), "bias"),
+                TensorNeed(self.name + ".alpha", (), "vector")]
+
+    def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
+        self.weight, self.bias = weights[self.name], weights[self.name + ".b"]
+        # the scalar stays on the device, as float32 whatever it was stored as
+        self.alpha = weights[self.name + ".alpha"].to(torch.float32).reshape(1)
+        self.rt = rt
+
+    def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None,
+                n_rows: Optional[int] = None, pending=None) -> torch.Tensor:
+        R = n_rows if n_rows is not None else (rows.numel() if rows is not None else x.shape[0])
+        out = torch.empty((R, self.size), dtype=self.rt.dtype, device=x.device)
+        K.dynamic_tanh(x, self.weight, self.bias, self.alpha, out, rows, R,
+                       pending.partial if pending is not None else None)
+        return out
+
+
 NORMS.register("rmsnorm", RmsNorm)
+NORMS.register("dynamic_tanh", DynamicTanh)

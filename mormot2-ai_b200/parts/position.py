@@ -5,6 +5,14 @@ product inv_freq[i] · pos.
 ``rope_half`` is the rotary encoding in the rotate-half pairing (i, i + rot_dim/2) with
 inv_freq[i] = 1 / f32(theta ^ f32(2i / rot_dim)), each step rounded to float32 as the
 reference does (``decoder.pas:1733-1736``; angles ``:2539-2561``). ``none`` rotates nothing.
+
+``rope_yarn`` is the same rotation with YaRN's frequencies: with
+d(t) = dims · ln(original / (2π t)) / (2 ln theta), lo = max(floor(d(fast)), 0),
+hi = min(ceil(d(slow)), dims − 1) and ramp_i = clamp((i − lo) / max(hi − lo, 0.001), 0, 1),
+frequency i is f_i · ((1 − ramp_i) + ramp_i / factor): fast-turning pairs keep their
+frequency, slow ones are stretched by ``factor``. Cosine and sine are both multiplied by
+``amplitude`` = 0.1 · ln(factor) + 1. An encoding's ``amplitude`` is 1 unless it says
+otherwise; a mixer passes it to the kernel that rotates.
 """
 from __future__ import annotations
 
@@ -29,6 +37,7 @@ def rope_inverse_frequencies(theta: float, rot_dim: int) -> np.ndarray:
 
 class RopeHalf(Part):
     capturable = True
+    amplitude = 1.0
 
     def __init__(self, spec, prefix: str = ""):
         super().__init__(spec, prefix)
@@ -46,12 +55,46 @@ class RopeHalf(Part):
         return self.inv_freq, self.rot_dim
 
 
+def yarn_inverse_frequencies(theta: float, rot_dim: int, factor: float, original: float,
+                             fast: float, slow: float) -> np.ndarray:
+    """Float64 arithmetic, rounded to float32 once at the end."""
+    half = rot_dim // 2
+    i = np.arange(half, dtype=np.float64)
+    f = np.exp(-np.log(theta) * 2.0 * i / rot_dim)
+
+    def dim_of(turns: float) -> float:
+        return rot_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(dim_of(fast)), 0)
+    hi = min(math.ceil(dim_of(slow)), rot_dim - 1)
+    ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return (f / factor * ramp + f * (1.0 - ramp)).astype(np.float32)
+
+
+class RopeYarn(RopeHalf):
+    def __init__(self, spec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.factor, self.original = float(p["factor"]), float(p["original"])
+        self.fast, self.slow = float(p["fast"]), float(p["slow"])
+        if min(self.factor, self.original, self.fast, self.slow) <= 0:
+            raise ConfigError("YaRN scaling: factor, original, fast and slow are positive")
+        self.amplitude = 0.1 * math.log(self.factor) + 1.0
+
+    def bind(self, weights, rt) -> None:
+        self.inv_freq = torch.from_numpy(yarn_inverse_frequencies(
+            self.theta, self.rot_dim, self.factor, self.original, self.fast,
+            self.slow)).to(rt.device)
+
+
 class NoPosition(Part):
     capturable = True
+    amplitude = 1.0
 
     def frequencies(self) -> Tuple[Optional[torch.Tensor], int]:
         return None, 0
 
 
 POSITIONS.register("rope_half", RopeHalf)
+POSITIONS.register("rope_yarn", RopeYarn)
 POSITIONS.register("none", NoPosition)
