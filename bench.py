@@ -1,6 +1,7 @@
 """Measures decoding and prefill of the Qwen3-8B shape with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --design busavik [--sizes small,mid]     (another workload, see below)
 
 A step is one decode step of a batch of 8 sequences whose context reaches 4,096 at the end of
 the timed steps. ``value`` is decoded tokens a second with the steps running back to back on
@@ -16,6 +17,11 @@ Beside the headline: ``prefill`` (2,048 tokens), ``points`` (tokens/s of decode 
 and 64, of prefills of 8,192 and 16,384 tokens, of the Qwen3-0.6B shape with 64 unequal
 prompts, and of the Qwen3-32B shape) with ``points_detail`` (each point's ms, bytes or flops,
 fraction of the measured peak and its own clock samples).
+
+``--design busavik`` leaves all of that aside and measures the Busavik design (latent
+attention, Dynamic Tanh, routed experts) at layer sizes of real models beside the Qwen3 model
+of equal size: prefill and decode tokens/s, and the kernels of a step by class against what
+each class must compute or read.
 """
 import argparse
 import json
@@ -337,6 +343,142 @@ def other_shapes(torch, a, pts):
     torch.cuda.empty_cache()
 
 
+# ------------------------------------------------------------------ --design busavik
+def busavik_shapes(name):
+    """A Busavik configuration whose layers have the sizes of a real model's (one layer with a
+    dense and one with a routed feed-forward) and the Qwen3 configuration of equal width, head
+    count, head size, feed-forward size and layer count, the closest model of this library."""
+    from mormot2_ai_b200 import BusavikConfig, Qwen3Config
+    sizes = {
+        # width, heads, dim, rot, vdim, kv_rank, q_rank, dense ff, experts, top, expert ff, shared ff
+        "small": (1024, 8, 64, 32, 64, 256, 384, 4096, 16, 2, 1024, 1024),
+        "mid": (2048, 16, 128, 64, 128, 512, 768, 8192, 64, 6, 1408, 2816),
+    }[name]
+    w, h, dim, rd, vd, kvr, qr, ff, ne, top, eff, sff = sizes
+    mixer = {"heads": h, "dim": dim, "rot_dim": rd, "vdim": vd, "kv_rank": kvr, "q_rank": qr,
+             "scale": (dim + rd) ** -0.5,
+             "rot": {"base": 10000.0, "dims": rd,
+                     "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    vocab = 32768
+    doc = {"architecture": "Busavik", "vocab": vocab, "width": w, "norm": {"eps": 1e-6},
+           "logit_scale": 1.0,
+           "layers": [{"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}},
+                      {"type": "latent_attention", "mixer": mixer,
+                       "mlp": {"kind": "moe", "expert": {"ff": eff},
+                               "router": {"experts": ne, "top": top}, "shared": {"ff": sff}}}]}
+    twin = Qwen3Config(vocab_size=vocab, hidden_size=w, num_hidden_layers=2,
+                       num_attention_heads=h, num_key_value_heads=max(1, h // 4),
+                       head_dim=dim + rd if dim + rd in (64, 128) else 128,
+                       intermediate_size=ff, max_position_embeddings=40960, rms_norm_eps=1e-6,
+                       rope_theta=1e6, tie_word_embeddings=False)
+    return BusavikConfig.from_dict(doc), twin
+
+
+def busavik_work(cfg, tokens, batch, held):
+    """Multiply-add work (FLOPs) of a prefill of one prompt of ``tokens`` tokens and bytes that a
+    decode step of ``batch`` sequences holding ``held`` tokens together must read, by class of
+    kernel, for either family. Attention of the latent form counts what its kernel does: every
+    head scores rows of kv_rank + rot_dim values and sums rows of kv_rank values."""
+    pairs = tokens * (tokens + 1) / 2
+    out = {"prefill_flops": {"attention": 0.0, "products": 0.0},
+           "decode_bytes": {"attention": 0.0, "products": 0.0}}
+    if hasattr(cfg, "layers"):
+        w = cfg.width
+        for layer in cfg.layers:
+            m, mlp = layer["mixer"], layer["mlp"]
+            h, dim, rd, vd, kvr, qr = (m[k] for k in ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank"))
+            dense = (qr + kvr + rd + h * vd) * w + h * (dim + rd) * qr + h * vd * w
+            per_head = h * dim * kvr + h * vd * kvr
+            if mlp["kind"] == "dense":
+                ff_params = ff_read = 3 * w * mlp["ff"]
+            else:
+                e, top = mlp["router"]["experts"], mlp["router"]["top"]
+                one = 3 * w * mlp["expert"]["ff"]
+                shared = 3 * w * mlp["shared"]["ff"] + w
+                ff_params = top * one + shared + e * w
+                ff_read = min(e, batch * top) * one + shared + e * w
+            out["prefill_flops"]["products"] += 2 * tokens * (dense + per_head + ff_params)
+            out["prefill_flops"]["attention"] += 2 * h * (kvr + rd + kvr) * pairs
+            out["decode_bytes"]["products"] += 2 * (dense + per_head + ff_read)
+            out["decode_bytes"]["attention"] += 2 * held * (kvr + rd)
+        out["prefill_flops"]["products"] += 2 * cfg.vocab * w
+        out["decode_bytes"]["products"] += 2 * cfg.vocab * w
+    else:
+        h, i = cfg.hidden_size, cfg.intermediate_size
+        per_layer = (cfg.q_width + 2 * cfg.kv_width) * h + h * cfg.q_width + 3 * h * i
+        n = cfg.num_hidden_layers
+        out["prefill_flops"]["products"] = n * 2 * tokens * per_layer + 2 * cfg.vocab_size * h
+        out["prefill_flops"]["attention"] = n * 4 * cfg.q_width * pairs
+        out["decode_bytes"]["products"] = 2 * (n * per_layer + cfg.vocab_size * h)
+        out["decode_bytes"]["attention"] = n * 2 * held * 2 * cfg.kv_width
+    return out
+
+
+def busavik_bench(a):
+    """Prefill and decode of the Busavik design beside the Qwen3 model of equal size: tokens/s
+    of the product path (prefill step; decode steps as CUDA graphs on the device), and the
+    kernels of one prefill and one decode step timed by class (``Engine.timed_step``) against
+    what each class must compute or read."""
+    import torch
+    from mormot2_ai_b200 import Engine, Entry
+    from mormot2_ai_b200.sampling import DeviceSampler, Sampling
+    pk = peaks()
+    tokens, batch, ctx = a.busavik_prefill, 8, a.busavik_context
+    steps, warm = min(a.steps, 64), max(a.warmup, 3)
+    points = {}
+    for size in [v for v in a.sizes.split(",") if v]:
+        for family, cfg in zip(("busavik", "qwen3"), busavik_shapes(size)):
+            eng = Engine.from_random(cfg, seed=5, std=0.02, max_tokens=batch * ctx + tokens,
+                                     max_context=max(ctx, tokens), max_slots=batch,
+                                     prefill_chunk=4096, max_step_tokens=8192)
+            sampler = DeviceSampler(eng.rt.device, eng.max_slots, eng.vocab_size)
+            work = busavik_work(cfg, tokens, batch, batch * (ctx - steps / 2.0))
+            pms, pclocks = clocked(timed_prefill, torch, eng, [tokens])
+            lens = [ctx - steps - warm - SETTLE] * batch
+            (dms, held, launches), dclocks = clocked(timed_decode, torch, eng, sampler, Sampling(),
+                                                     lens, steps, warm, 60)
+            # the kernels by class, run one by one: one prefill, then decode steps at the context
+            gen = torch.Generator().manual_seed(9)
+            slot = eng.open()
+            prompt = torch.randint(0, eng.vocab_size, (tokens,), generator=gen).tolist()
+            eng.timed_step([Entry(slot, prompt)])                       # warms the kernels up
+            eng.truncate(slot, 0)
+            _, pshares, _ = eng.timed_step([Entry(slot, prompt)])
+            eng.close(slot)
+            slots = [eng.open() for _ in range(batch)]
+            eng.step([Entry(s, torch.randint(0, eng.vocab_size, (ctx - 8,), generator=gen).tolist())
+                      for s in slots])
+            dshares = {}
+            for k in range(6):
+                _, sh, _ = eng.timed_step([Entry(s, [1 + k]) for s in slots])
+                if k >= 2:
+                    for name, ms in sh.items():
+                        dshares[name] = dshares.get(name, 0.0) + ms / 4
+            eng.rt.check()
+            flops, nbytes = work["prefill_flops"], work["decode_bytes"]
+            points[f"{size}_{family}"] = {
+                "prefill_tokens_per_s": round(tokens / (pms / 1e3), 1), "prefill_ms": round(pms, 3),
+                "decode_tokens_per_s": round(batch * steps / (dms / 1e3), 1),
+                "decode_ms_per_step": round(dms / steps, 4), "decode_launches_per_step": launches // steps,
+                "prefill_frac_bf16": round(sum(flops.values()) / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                "decode_frac_hbm": round(sum(nbytes.values()) / (dms / steps / 1e3) / (pk["hbm_gbs"] * 1e9), 4),
+                "prefill_kernels_ms": {k: round(v, 4) for k, v in sorted(pshares.items())},
+                "decode_kernels_ms": {k: round(v, 4) for k, v in sorted(dshares.items())},
+                "prefill_class_frac_bf16": {
+                    k: round(flops[k] / (pshares[k] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)
+                    for k in flops if pshares.get(k)},
+                "decode_class_frac_hbm": {
+                    k: round(nbytes[k] / (dshares[k] / 1e3) / (pk["hbm_gbs"] * 1e9), 4)
+                    for k in nbytes if dshares.get(k)},
+                "clocks": {"prefill": pclocks, "decode": dclocks}}
+            del eng, sampler
+            torch.cuda.empty_cache()
+    print(json.dumps({"design": "busavik", "beside": "qwen3 of equal width, heads and feed-forward",
+                      "prefill_tokens": tokens, "decode_batch": batch, "decode_context": ctx,
+                      "dtype": "bf16", "data": "synthetic", "peaks": pk, "points": points}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -353,7 +495,16 @@ def main():
                     help="token counts of the long prefill points (one sequence each)")
     ap.add_argument("--only-prefill", type=int, nargs="?", const=PREFILL_TOKENS, default=0,
                     help="only a prefill of this many tokens (for profiles; prints a short line)")
+    ap.add_argument("--design", default="", choices=["", "busavik"],
+                    help="busavik: instead of the default workload, prefill and decode of the "
+                         "Busavik design at layer sizes of real models beside the Qwen3 model of "
+                         "equal size (prints its own JSON line)")
+    ap.add_argument("--sizes", default="small,mid", help="with --design: which layer sizes")
+    ap.add_argument("--busavik-prefill", type=int, default=2048)
+    ap.add_argument("--busavik-context", type=int, default=2048)
     a = ap.parse_args()
+    if a.design == "busavik" and a.impl == "ours" and a.gpus == 1:
+        return busavik_bench(a)
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "the reference is Free Pascal / Delphi source without a Python package; "

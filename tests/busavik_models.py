@@ -96,5 +96,5 @@ class SmallModel:
         rng = np.random.default_rng(1000 * self.seed + seed)
         return rng.integers(0, self.doc["vocab"], n).tolist()
 
-    def reference(self, ids, states=None):
-        return self.plain.forward(self.plain_config, self.weights, ids, states)
+    def reference(self, ids, states=None, routing=None):
+        return self.plain.forward(self.plain_config, self.weights, ids, states, routing)

@@ -128,9 +128,44 @@ def route(z, top: int):
     return order, e / e.sum(axis=-1, keepdims=True)
 
 
-def moe_ff(h, mlp: Dict, W, prefix: str):
+class Routing:
+    """What a test wants to know of the routers' choices, or to settle about them.
+
+    ``margins[(run, t)]``: how far the last chosen logit of token t in layer run ``run`` lies
+    above the first one left out, in units of the spread (standard deviation) of the token's
+    logits. ``forced[(run, t)]``: experts that another implementation chose there; they
+    replace the plain choice where the two differ and the margin is below ``close`` (a
+    computation in 16 bits may fall on either side of such a call), and where the margin is
+    larger the difference is an error."""
+
+    def __init__(self, forced=None, close: float = 0.03):
+        self.forced = forced or {}
+        self.close = close
+        self.margins: Dict = {}
+        self.replaced: List = []
+
+
+def moe_ff(h, mlp: Dict, W, prefix: str, routing: Optional[Routing] = None, run: int = 0):
     top = int(mlp["router"]["top"])
-    chosen, weight = route(h @ W[prefix + "router"].T, top)
+    z = h @ W[prefix + "router"].T
+    chosen, weight = route(z, top)
+    if routing is not None:
+        for t in range(h.shape[0]):
+            zs = np.sort(z[t])[::-1]
+            margin = (zs[top - 1] - zs[top]) / max(z[t].std(), 1e-30) if top < len(zs) else np.inf
+            routing.margins[(run, t)] = float(margin)
+            theirs = routing.forced.get((run, t))
+            if theirs is not None and set(int(e) for e in theirs) != set(chosen[t].tolist()):
+                if margin >= routing.close:
+                    raise AssertionError(f"run {run}, token {t}: experts {sorted(theirs)} were "
+                                         f"chosen, {sorted(chosen[t].tolist())} expected, at a "
+                                         f"margin of {margin:.3g}")
+                order = sorted((int(e) for e in theirs), key=lambda e: (-z[t, e], e))
+                chosen[t] = order
+                zc = z[t, order]
+                e = np.exp(zc - zc.max())
+                weight[t] = e / e.sum()
+                routing.replaced.append((run, t))
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
         for k in range(top):
@@ -142,12 +177,12 @@ def moe_ff(h, mlp: Dict, W, prefix: str):
     return out
 
 
-def feed_forward(h, mlp: Optional[Dict], W, prefix: str):
+def feed_forward(h, mlp: Optional[Dict], W, prefix: str, routing=None, run: int = 0):
     if mlp is None:
         return np.zeros_like(h)
     if mlp.get("kind", "dense") == "dense":
         return dense_ff(h, W, prefix)
-    return moe_ff(h, mlp, W, prefix)
+    return moe_ff(h, mlp, W, prefix, routing, run)
 
 
 # ---------------------------------------------------------------------------- the model
@@ -164,19 +199,22 @@ def norm_of(x, W, name: str):
     return dynamic_tanh(x, W[name], W[name + ".b"], float(W[name + ".alpha"]))
 
 
-def forward(config: Dict, W: Dict[str, np.ndarray], tokens, states: Optional[list] = None):
+def forward(config: Dict, W: Dict[str, np.ndarray], tokens, states: Optional[list] = None,
+            routing: Optional[Routing] = None):
     """Logits [T, vocab] of one sequence from position 0. ``states``: a list that receives the
-    residual after every layer run."""
+    residual after every layer run. ``routing``: see ``Routing``; a run is counted by its
+    place in the order of layer runs."""
     eps = float(config["norm"]["eps"])
     x = W["embed"][np.asarray(tokens)]
-    for i in layer_order(config):
+    for run, i in enumerate(layer_order(config)):
         layer = config["layers"][i]
         p = f"l{i}."
         if layer["type"] != "latent_attention":
             raise ValueError(layer["type"])
         x = x + latent_attention(norm_of(x, W, p + "norm1"), layer["mixer"], W, p + "mix.", eps)
         if layer.get("mlp") is not None:
-            x = x + feed_forward(norm_of(x, W, p + "norm2"), layer["mlp"], W, p + "mlp.")
+            x = x + feed_forward(norm_of(x, W, p + "norm2"), layer["mlp"], W, p + "mlp.",
+                                 routing, run)
         if states is not None:
             states.append(x.copy())
     return norm_of(x, W, "final.norm") @ W["head"].T * float(config["logit_scale"])
