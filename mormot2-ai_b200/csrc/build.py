@@ -49,11 +49,15 @@ SOURCES = {
     "attention_tc": "attention_tc.cu",
     "latent": "latent.cu",
     "moe": "moe.cu",
+    "latent_mma": "latent_mma.cu",
 }
 HEADERS = ["common.cuh"]
 EXTRA_HEADERS = {"gemm_tc": ["tc_common.cuh"],
                  "attention_mma": ["mma_common.cuh", "tc_common.cuh", "no_alloc.h"],
-                 "attention_tc": ["tc_common.cuh"]}
+                 "attention_tc": ["tc_common.cuh"],
+                 "latent": ["mma_common.cuh", "mma_tile.cuh"],
+                 "moe": ["mma_common.cuh", "mma_tile.cuh"],
+                 "latent_mma": ["mma_common.cuh"]}
 
 _lock = threading.Lock()
 _loaded: Dict[str, ctypes.CDLL] = {}

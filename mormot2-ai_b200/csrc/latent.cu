@@ -17,6 +17,7 @@
 //                     columns, or a sigmoid gate on C
 //   latent_attention  causal softmax attention of every head over the rows of the cache
 #include "common.cuh"
+#include "mma_tile.cuh"
 
 MB_DEFINE_LAST_ERROR
 
@@ -214,6 +215,60 @@ heads_gemm_kernel(const T* __restrict__ A, int lda, int lda_h, const TB* __restr
   }
 }
 
+// The same product on the tensor cores for bfloat16 operands (mma_tile.cuh): a block computes
+// 64 tokens x 64 outputs of one head. The gate and the rotated tail as above (the tail is
+// read from global memory, value and partner).
+__global__ void __launch_bounds__(128)
+heads_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, int lda_h,
+                      const __nv_bfloat16* __restrict__ B, __nv_bfloat16* __restrict__ C, int ldc,
+                      int ldc_h, int M, int N, int K, const __nv_bfloat16* __restrict__ gate,
+                      int ldg, int tail, int rot_dims, const float* __restrict__ inv_freq,
+                      float amplitude, const int* __restrict__ tok_pos) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  __shared__ __align__(16) MtShared<1> sh;
+  const int h = blockIdx.z, m0 = blockIdx.y * MT_BM, n0 = blockIdx.x * MT_BN;
+  const __nv_bfloat16* Ah = A + (size_t)h * lda_h;
+  if (threadIdx.x < MT_BM) {
+    const int gm = m0 + threadIdx.x;
+    sh.a_rows[threadIdx.x] = gm < M ? Ah + (size_t)gm * lda : nullptr;
+  }
+  __syncthreads();
+  const __nv_bfloat16* b[1] = {B + ((size_t)h * N + n0) * K};
+  float acc[1][2][4][4];
+  mt_mainloop<1>(sh, b, min(MT_BN, N - n0), K, acc);
+  mt_for_each([&](int r, int c, int mi, int ni, int e) {
+    const int gm = m0 + r, gn = n0 + c;
+    if (gm >= M || gn >= N) return;
+    float v = acc[0][mi][ni][e];
+    if (gate) {
+      const float gv = __bfloat162float(gate[(size_t)gm * ldg + (size_t)h * N + gn]);
+      v *= 1.0f / (1.0f + expf(-gv));
+    }
+    C[(size_t)gm * ldc + (size_t)h * ldc_h + gn] = __float2bfloat16_rn(v);
+  });
+  if (tail > 0 && blockIdx.x == 0) {
+    const int half = rot_dims >> 1;
+    for (int e = threadIdx.x; e < MT_BM * tail; e += blockDim.x) {
+      const int r = e / tail, i = e % tail;
+      const int gm = m0 + r;
+      if (gm >= M) continue;
+      const __nv_bfloat16* src = Ah + (size_t)gm * lda + K;
+      float v = __bfloat162float(src[i]);
+      if (i < rot_dims) {
+        const int f = i < half ? i : i - half;
+        float sn, cs;
+        sincosf(inv_freq[f] * (float)tok_pos[gm], &sn, &cs);
+        sn *= amplitude;
+        cs *= amplitude;
+        const float other = __bfloat162float(src[i < half ? i + half : i - half]);
+        v = i < half ? v * cs - other * sn : v * cs + other * sn;
+      }
+      C[(size_t)gm * ldc + (size_t)h * ldc_h + N + i] = __float2bfloat16_rn(v);
+    }
+  }
+}
+
 MB_EXPORT int mb_heads_gemm(const void* A, int dtype, int lda, int lda_h, const void* B,
                             int b_dtype, void* C, int ldc, int ldc_h, int M, int N, int K,
                             int heads, const void* gate, int ldg, int tail, int rot_dims,
@@ -224,6 +279,17 @@ MB_EXPORT int mb_heads_gemm(const void* A, int dtype, int lda, int lda_h, const 
   if (tail > 0 && (rot_dims > tail || (rot_dims & 1) || (rot_dims > 0 && !inv_freq) || !tok_pos))
     MB_FAIL("mb_heads_gemm: %d rotating values of a tail of %d", rot_dims, tail);
   cudaStream_t s = (cudaStream_t)stream;
+  // bfloat16 operands whose rows start on 16-byte boundaries, and more than a few tokens: the
+  // tensor cores (a decode step's few rows stay with the kernel below, which streams each
+  // weight once with a sixteenth of the multiply-adds of a 64-row tile)
+  if (dtype == MB_BF16 && b_dtype == MB_BF16 && M > 16 && K % 8 == 0 && lda % 8 == 0 &&
+      lda_h % 8 == 0 && (((uintptr_t)A | (uintptr_t)B) & 15) == 0) {
+    mb_launch(heads_gemm_mma_kernel, dim3((N + MT_BN - 1) / MT_BN, (M + MT_BM - 1) / MT_BM, heads),
+              dim3(128), 0, s, (const __nv_bfloat16*)A, lda, lda_h, (const __nv_bfloat16*)B,
+              (__nv_bfloat16*)C, ldc, ldc_h, M, N, K, (const __nv_bfloat16*)gate, ldg, tail,
+              rot_dims, inv_freq, amplitude, tok_pos);
+    MB_CHECK_LAUNCH("mb_heads_gemm");
+  }
 #define GO(T_, TB_, BM_)                                                                     \
   mb_launch(heads_gemm_kernel<T_, TB_, BM_>, dim3((N + HG_BN - 1) / HG_BN, (M + BM_ - 1) / BM_, \
                                                   heads),                                    \

@@ -16,6 +16,7 @@
 // The order of an expert's rows in its list comes from atomic counters and may differ from run
 // to run; no result depends on it (a row's sums are formed alone, in a fixed order).
 #include "common.cuh"
+#include "mma_tile.cuh"
 
 MB_DEFINE_LAST_ERROR
 
@@ -235,6 +236,54 @@ moe_gemm_kernel(const T* __restrict__ in, const TW* __restrict__ W, void* __rest
   }
 }
 
+// The same two products on the tensor cores for bfloat16 operands (mma_tile.cuh); the plan's
+// tiles have 64 rows. The first product multiplies the gathered rows with the gate and the up
+// rows of the expert at once.
+template <bool UP>
+__global__ void __launch_bounds__(128)
+moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ W,
+                    void* __restrict__ out, const int* __restrict__ plan, int A, int E,
+                    int max_tiles, int top, int N, int K, int act,
+                    const float* __restrict__ weight) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  constexpr int NB = UP ? 2 : 1;
+  const int tile = blockIdx.y;
+  if (tile >= plan[0]) return;
+  const int* offsets = plan + 1;
+  const int* perm = offsets + E + 1;
+  const int e = perm[A + tile];
+  const int r0 = perm[A + max_tiles + tile];
+  const int rows = min(MT_BM, offsets[e + 1] - r0);
+  __shared__ __align__(16) MtShared<NB> sh;
+  __shared__ int src[MT_BM];
+  if (threadIdx.x < MT_BM) {
+    const int r = threadIdx.x;
+    const int a = r < rows ? perm[r0 + r] : -1;
+    src[r] = a;
+    sh.a_rows[r] = a < 0 ? nullptr : in + (UP ? (size_t)(a / top) : (size_t)(r0 + r)) * K;
+  }
+  __syncthreads();
+  const int n0 = blockIdx.x * MT_BN;
+  const __nv_bfloat16* We = W + (size_t)e * NB * N * K;
+  const __nv_bfloat16* b[NB];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) b[nb] = We + ((size_t)nb * N + n0) * K;
+  float acc[NB][2][4][4];
+  mt_mainloop<NB>(sh, b, min(MT_BN, N - n0), K, acc);
+  mt_for_each([&](int r, int c, int mi, int ni, int el) {
+    const int gn = n0 + c;
+    if (r >= rows || gn >= N) return;
+    if (UP) {
+      ((__nv_bfloat16*)out)[(size_t)(r0 + r) * N + gn] =
+          __float2bfloat16_rn(moe_act(acc[0][mi][ni][el], act) * acc[NB - 1][mi][ni][el]);
+    } else {
+      const int a = src[r];
+      ((float*)out)[(size_t)a * N + gn] = weight[a] * acc[0][mi][ni][el];
+    }
+  });
+}
+
 MB_EXPORT int mb_moe_gemm(const void* in, int dtype, const void* W, int w_dtype, void* out,
                           const int* plan, int A, int E, int max_tiles, int bm, int top, int N,
                           int K, int up, int act, const float* weight, void* stream) {
@@ -243,6 +292,16 @@ MB_EXPORT int mb_moe_gemm(const void* in, int dtype, const void* W, int w_dtype,
   if (!up && weight == nullptr) MB_FAIL("mb_moe_gemm: the second product needs the weights");
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid((N + MG_BN - 1) / MG_BN, max_tiles);
+  if (dtype == MB_BF16 && w_dtype == MB_BF16 && bm == 64 && K % 8 == 0 &&
+      (((uintptr_t)in | (uintptr_t)W) & 15) == 0) {
+    if (up)
+      mb_launch(moe_gemm_mma_kernel<true>, grid, dim3(128), 0, s, (const __nv_bfloat16*)in,
+                (const __nv_bfloat16*)W, out, plan, A, E, max_tiles, top, N, K, act, weight);
+    else
+      mb_launch(moe_gemm_mma_kernel<false>, grid, dim3(128), 0, s, (const __nv_bfloat16*)in,
+                (const __nv_bfloat16*)W, out, plan, A, E, max_tiles, top, N, K, act, weight);
+    MB_CHECK_LAUNCH("mb_moe_gemm");
+  }
 #define GO(T_, TW_, BM_, UP_)                                                                \
   mb_launch(moe_gemm_kernel<T_, TW_, BM_, UP_>, grid, dim3(256), 0, s, (const T_*)in,        \
             (const TW_*)W, out, plan, A, E, max_tiles, top, N, K, act, weight)

@@ -128,6 +128,26 @@ class Runtime:
         return libs
 
     def latent_attention(self, q, out, step, line, nh, kv_rank, rot_dim, window, scale) -> None:
+        """Attention over a cache of latent rows: the tensor-core kernel for bfloat16 and sizes
+        it takes, else the float32 kernel. A decode step of few sequences deals a sequence's
+        key tiles out over several blocks; how many depends on the batch, the head count and
+        the most pages a sequence can hold only (a captured launch stays valid)."""
+        dk = kv_rank + rot_dim
+        if (self.fast_kernels and q.dtype == torch.bfloat16 and dk % 16 == 0
+                and kv_rank % 16 == 0 and kv_rank <= 512 and q.stride(0) % 8 == 0
+                and q.data_ptr() % 16 == 0 and (dk + 8) * 2 * 128 + 6144 <= 220 * 1024):
+            splits = 1
+            if step.decode:
+                from ..cache.pages import PAGE, pages_for
+                pages = line.max_pages
+                if window > 0:
+                    pages = min(pages, pages_for(window) + 1)
+                blocks = step.B * (-(-nh // 64))
+                room = self.attention_scratch.numel() // max(1, step.T * nh * (kv_rank + 2))
+                splits = max(1, min(self.sms // blocks, pages * (PAGE // 32), 16, room))
+            K.latent_attention_mma(q, out, step, line, nh, kv_rank, rot_dim, window, scale,
+                                   splits, self.attention_scratch if splits > 1 else None)
+            return
         K.latent_attention(q, out, step, line, nh, kv_rank, rot_dim, window, scale)
 
     def attention(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale) -> None:

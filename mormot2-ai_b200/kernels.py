@@ -70,6 +70,7 @@ CLASS_OF = {"mb_gemm_tc": "products", "mb_gemm_simt": "products",
             "mb_advance_decode": "sampling", "mb_dynamic_tanh": "norms",
             "mb_gated_act": "activation", "mb_scale": "activation", "mb_latent_prep": "rotary",
             "mb_heads_gemm": "products", "mb_latent_attention": "attention",
+            "mb_latent_attention_mma": "attention",
             "mb_moe_route": "routing", "mb_moe_plan": "routing", "mb_moe_gemm": "products",
             "mb_moe_combine": "routing"}
 
@@ -355,6 +356,26 @@ def latent_attention(q: torch.Tensor, out: torch.Tensor, step, line, nh: int, kv
           _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(line.k), code_of(out.dtype),
           _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(step.tok_slot),
           _ptr(step.tok_pos), T, nh, kv_rank, rot_dim, window, float(scale), _stream())
+
+
+def latent_attention_mma(q: torch.Tensor, out: torch.Tensor, step, line, nh: int, kv_rank: int,
+                         rot_dim: int, window: int, scale: float, splits: int,
+                         scratch: Optional[torch.Tensor]) -> None:
+    """``latent_attention`` on the tensor cores (bfloat16; kv_rank and kv_rank + rot_dim
+    multiples of 16, kv_rank at most 512). ``splits`` > 1: the key tiles of a sequence are
+    dealt out over that many blocks, whose partial results meet in ``scratch`` (float32)."""
+    T = out.shape[0]
+    _contig(out, "out"), _contig(q, "q")
+    assert q.dtype == out.dtype == line.k.dtype == torch.bfloat16
+    tiles = sum(-(-n * nh // 64) for n in step.host_new)
+    _call("latent_mma", "mb_latent_attention_mma",
+          [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i,
+           _vp, _ll, _vp],
+          _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.page_table),
+          line.max_pages, line.ring_pages, _ptr(step.seq_start), _ptr(step.seq_past),
+          _ptr(step.seq_slot), step.B, T, tiles, nh, kv_rank, rot_dim, window, float(scale),
+          splits, _ptr(scratch), scratch.numel() if scratch is not None else 0, _stream(),
+          launches=2 if splits > 1 else 1)
 
 
 # ------------------------------------------------------------------------------ routed experts

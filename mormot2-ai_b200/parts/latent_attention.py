@@ -47,7 +47,7 @@ class LatentAttention(Part):
             raise ConfigError(f"latent attention with sizes {p}")
 
     def libraries(self, rt) -> List[str]:
-        return ["latent"]
+        return ["latent", "latent_mma"] if rt.fast_kernels else ["latent"]
 
     def tensors(self) -> List[TensorNeed]:
         n = self.names

@@ -48,6 +48,9 @@ class RoutedExperts(Part):
         self.n_shared = prefix + names["shared"]
         self.n_shared_gate = prefix + names["shared_gate"]
         self.leaf = {k: names[k] for k in ("gate", "up", "down")}
+        # for tests and debugging: called with (part, step, chosen experts [T, top] on the
+        # device) in every forward; while it is set the part is not captured into graphs
+        self.probe = None
 
     def libraries(self, rt) -> List[str]:
         return ["moe"]
@@ -95,7 +98,15 @@ class RoutedExperts(Part):
             g, u = take(self.n_shared + l["gate"]), take(self.n_shared + l["up"])
             if g.dtype != u.dtype:
                 g, u = g.float(), u.float()
-            self.shared_up = Linear(torch.cat([g, u], dim=0), rt)
+            # SiLU: gate and up rows alternate and the product's epilogue applies the activation
+            # (as the SwiGLU feed-forward does); another activation: gate rows, then up rows,
+            # and the activation kernel after the product
+            self.shared_fused = self.act == K.ACT_SILU
+            if self.shared_fused:
+                both = torch.stack([g, u], dim=1).reshape(2 * self.shared_size, self.hidden)
+            else:
+                both = torch.cat([g, u], dim=0)
+            self.shared_up = Linear(both, rt, swiglu=self.shared_fused)
             self.shared_down = Linear(weights[self.n_shared + l["down"]], rt)
 
     def forward(self, h, x, step):
@@ -107,7 +118,13 @@ class RoutedExperts(Part):
         w = torch.empty((T, top), dtype=torch.float32, device=dev)
         sg = torch.empty((T,), dtype=torch.float32, device=dev) if self.shared_size else None
         K.moe_route(z, E, top, E, ids, w, sg)
-        bm = 16 if A <= 16 * E else 64
+        if self.probe is not None:
+            self.probe(self, step, ids)
+        # rows per tile of an expert's list: 64 where the tensor-core kernel runs (bfloat16), else
+        # 16 while an expert has few rows (a decode step), so that few multiply-adds are wasted
+        fast = self.rt.fast_kernels and self.w_up.dtype == torch.bfloat16 and self.hidden % 8 == 0 \
+            and self.inter % 8 == 0
+        bm = 64 if fast or A > 16 * E else 16
         max_tiles = (A + bm - 1) // bm + E
         plan = torch.empty((2 + E + A + 2 * max_tiles,), dtype=torch.int32, device=dev)
         K.moe_plan(ids, E, bm, max_tiles, plan)
@@ -117,9 +134,12 @@ class RoutedExperts(Part):
         K.moe_gemm(act, self.w_down, y, plan, A, max_tiles, bm, top, False, self.act, w)
         shared = None
         if self.shared_size:
-            gu = self.shared_up(h)
-            sa = torch.empty((T, self.shared_size), dtype=self.rt.dtype, device=dev)
-            K.gated_act(gu, sa, self.act)
+            if self.shared_fused:
+                sa = self.shared_up(h)
+            else:
+                gu = self.shared_up(h)
+                sa = torch.empty((T, self.shared_size), dtype=self.rt.dtype, device=dev)
+                K.gated_act(gu, sa, self.act)
             shared = self.shared_down(sa, out_dtype=torch.float32)
         K.moe_combine(x, y, top, shared, sg)
         return None

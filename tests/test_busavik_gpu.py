@@ -198,10 +198,11 @@ def test_latent_prep_kernel_writes_normed_latents_and_the_rotated_part(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("M", [3, 70])
-def test_heads_gemm_kernel(dtype, M):
+@pytest.mark.parametrize("M,Kd,tail", [(3, 10, 6), (70, 10, 6), (150, 40, 8)])
+def test_heads_gemm_kernel(dtype, M, Kd, tail):
+    """The last case has rows on 16-byte boundaries and goes to the tensor cores in bfloat16."""
     rng = np.random.default_rng(4)
-    H, N, Kd, tail, dims = 3, 21, 10, 6, 4
+    H, N, dims = 3, 21, 4
     t = TORCH[dtype]
     a = rng.normal(size=(M, H, Kd + tail))
     b = rng.normal(size=(H, N, Kd))
@@ -255,13 +256,79 @@ def test_latent_attention_kernel_random_rows(dtype, sizes):
         assert np.abs(got[i] - want).max() < tol * max(1.0, np.abs(want).max()), i
 
 
+@pytest.mark.parametrize("sizes", [(5, 32, 16), (16, 64, 32), (3, 160, 32), (70, 48, 16)])
+def test_latent_attention_tensor_core_kernel(sizes):
+    """The tensor-core kernel: two prompts' portions behind unequal pasts in one step (rows of
+    several tokens and heads in one block, tiles of keys across page borders), then single
+    tokens with a sequence's key tiles dealt out over 1, 3 and 16 blocks."""
+    nh, kvr, rd = sizes
+    rng = np.random.default_rng(11)
+    t = torch.bfloat16
+    line = latent_line(3, 512, kvr + rd, t, seed=12)
+    pasts, news = [130, 0, 61], [37, 70, 5]
+    rows = [rng.normal(size=(p + n, kvr + rd)) for p, n in zip(pasts, news)]
+    for slot, r in enumerate(rows):
+        write_rows(line, slot, r)
+    q = [rng.normal(size=(n, nh, kvr + rd)) for n in news]
+    step = make_step([(slot, pasts[slot], [0] * news[slot], []) for slot in range(3)])
+    T = sum(news)
+    out = torch.empty((T, nh * kvr), dtype=t, device=DEV)
+    K.latent_attention_mma(dev(np.concatenate(q).reshape(T, -1), t), out, step, line, nh, kvr, rd,
+                           0, 0.2, 1, None)
+    got = out.float().cpu().numpy().reshape(T, nh, kvr)
+    at = 0
+    for slot in range(3):
+        rr = rounded(rows[slot], "bfloat16")
+        for i in range(news[slot]):
+            want = plain_latent_attention(rounded(q[slot][i], "bfloat16"),
+                                          rr[:pasts[slot] + i + 1], kvr, 0.2)
+            assert np.abs(got[at] - want).max() < 2e-2 * max(1.0, np.abs(want).max()), (slot, i)
+            at += 1
+    # decode: one token of every sequence, the keys of a sequence over several blocks
+    lens = [p + n for p, n in zip(pasts, news)]
+    step = make_step([(slot, lens[slot] - 1, [0], []) for slot in range(3)])
+    qd = rng.normal(size=(3, nh, kvr + rd))
+    scratch = torch.empty((3 * nh * 16 * (kvr + 2),), dtype=torch.float32, device=DEV)
+    for splits in (1, 3, 16):
+        out = torch.full((3, nh * kvr), 7.0, dtype=t, device=DEV)
+        K.latent_attention_mma(dev(qd.reshape(3, -1), t), out, step, line, nh, kvr, rd, 0, 0.2,
+                               splits, scratch)
+        got = out.float().cpu().numpy().reshape(3, nh, kvr)
+        for slot in range(3):
+            want = plain_latent_attention(rounded(qd[slot], "bfloat16"),
+                                          rounded(rows[slot], "bfloat16"), kvr, 0.2)
+            assert np.abs(got[slot] - want).max() < 2e-2 * max(1.0, np.abs(want).max()), (splits, slot)
+
+
+def test_the_runtime_sends_sizes_it_takes_to_the_tensor_cores():
+    from mormot2_ai_b200.engine.runtime import Runtime
+    rt = Runtime(torch.bfloat16)
+    calls = []
+    real = K.latent_attention_mma
+    K.latent_attention_mma = lambda *a, **k: (calls.append(a[9]), real(*a, **k))
+    try:
+        for (kvr, rd), fast in (((32, 16), True), ((40, 12), False)):
+            line = latent_line(1, 2048, kvr + rd, torch.bfloat16)
+            step = make_step([(0, 100, [0], [])])
+            q = torch.zeros((1, 4 * (kvr + rd)), dtype=torch.bfloat16, device=DEV)
+            out = torch.empty((1, 4 * kvr), dtype=torch.bfloat16, device=DEV)
+            calls.clear()
+            rt.latent_attention(q, out, step, line, 4, kvr, rd, 0, 1.0)
+            assert bool(calls) == fast
+            if fast:
+                assert calls[0] == 16          # one sequence, 148 SMs: the most splits
+    finally:
+        K.latent_attention_mma = real
+    rt.check()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("past", [63, 64, 700])
 def test_latent_attention_finds_one_far_key_and_no_later_one(dtype, past):
     """One key far back (the very first, one at a page border, one in the middle) is made to
     take all of a head's weight: the output must be that row's latent. A key that would take
     all the weight but lies AFTER the query's position must not be seen."""
-    nh, kvr, rd = 2, 16, 8
+    nh, kvr, rd = 2, 16, 16
     t = TORCH[dtype]
     rng = np.random.default_rng(7)
     line = latent_line(1, 1024, kvr + rd, t, seed=8)
@@ -278,17 +345,24 @@ def test_latent_attention_finds_one_far_key_and_no_later_one(dtype, past):
         q[0, :, kvr] = 1.0
         q[0, :, kvr + 1] = 2.0
         step = make_step([(0, past, [0], [])])     # the query stands at position `past`
-        out = torch.empty((1, nh * kvr), dtype=t, device=DEV)
-        K.latent_attention(dev(q.reshape(1, -1), t), out, step, line, nh, kvr, rd, 0, 1.0)
-        got = out.float().cpu().numpy().reshape(nh, kvr)
         want = rounded(rows2[target, :kvr], dtype)
-        assert np.abs(got - want).max() < 2e-2, (target, past)
+        for kernel in ["simt"] + (["mma 1", "mma 5"] if dtype == "bfloat16" else []):
+            out = torch.empty((1, nh * kvr), dtype=t, device=DEV)
+            if kernel == "simt":
+                K.latent_attention(dev(q.reshape(1, -1), t), out, step, line, nh, kvr, rd, 0, 1.0)
+            else:
+                splits = int(kernel.split()[1])
+                scratch = torch.empty((nh * splits * (kvr + 2),), dtype=torch.float32, device=DEV)
+                K.latent_attention_mma(dev(q.reshape(1, -1), t), out, step, line, nh, kvr, rd, 0,
+                                       1.0, splits, scratch)
+            got = out.float().cpu().numpy().reshape(nh, kvr)
+            assert np.abs(got - want).max() < 2e-2, (target, past, kernel)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_latent_attention_window_edges(dtype):
     """With a window the key just inside it is seen and the one just outside is not."""
-    nh, kvr, rd, window, past = 1, 8, 4, 70, 200
+    nh, kvr, rd, window, past = 1, 16, 16, 70, 200
     t = TORCH[dtype]
     line = latent_line(1, 256, kvr + rd, t, seed=9)
     rng = np.random.default_rng(9)
@@ -302,27 +376,33 @@ def test_latent_attention_window_edges(dtype):
         q = np.zeros((1, kvr + rd))
         q[0, kvr] = 1.0
         step = make_step([(0, past, [0], [])])
-        out = torch.empty((1, kvr), dtype=t, device=DEV)
-        K.latent_attention(dev(q, t), out, step, line, nh, kvr, rd, window, 1.0)
-        got = out.float().cpu().numpy()[0]
-        if seen:
-            assert np.abs(got - rounded(rows[loud, :kvr], dtype)).max() < 2e-2
-        else:
-            want = plain_latent_attention(rounded(q, dtype), rounded(rows, dtype), kvr, 1.0,
-                                          lo=inside)[0]
-            assert np.abs(got - want).max() < 2e-2
+        for kernel in ["simt"] + (["mma"] if dtype == "bfloat16" else []):
+            out = torch.empty((1, kvr), dtype=t, device=DEV)
+            if kernel == "simt":
+                K.latent_attention(dev(q, t), out, step, line, nh, kvr, rd, window, 1.0)
+            else:
+                K.latent_attention_mma(dev(q, t), out, step, line, nh, kvr, rd, window, 1.0, 1, None)
+            got = out.float().cpu().numpy()[0]
+            if seen:
+                assert np.abs(got - rounded(rows[loud, :kvr], dtype)).max() < 2e-2, kernel
+            else:
+                want = plain_latent_attention(rounded(q, dtype), rounded(rows, dtype), kvr, 1.0,
+                                              lo=inside)[0]
+                assert np.abs(got - want).max() < 2e-2, kernel
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,E,top,shared", [(3, 5, 1, 0), (9, 6, 3, 20), (150, 4, 2, 12)])
-def test_routed_experts_part(dtype, T, E, top, shared):
+@pytest.mark.parametrize("T,E,top,shared,ff", [(3, 5, 1, 0, 14), (9, 6, 3, 20, 14),
+                                               (150, 4, 2, 12, 14), (150, 4, 2, 16, 40),
+                                               (5, 7, 3, 8, 16)])
+def test_routed_experts_part(dtype, T, E, top, shared, ff):
     """The whole routed feed-forward (router, lists, both products, the sum) against the plain
     one; the router's rows are scaled so that no choice is a close call."""
     from mormot2_ai_b200.config.spec import PartSpec
     from mormot2_ai_b200.engine.runtime import Runtime
     from mormot2_ai_b200.parts import FEED_FORWARDS
     rng = np.random.default_rng(10 + T)
-    H, ff = 24, 14
+    H = 24            # with ff a multiple of 8 the bfloat16 products run on the tensor cores
     t = TORCH[dtype]
     names = {"router": "router", "expert": "e{}.", "shared": "shared.",
              "shared_gate": "shared.sg", "gate": "gate", "up": "up", "down": "down"}
