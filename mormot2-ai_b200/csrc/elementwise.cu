@@ -300,11 +300,14 @@ MB_EXPORT int mb_advance_decode(int* tok_ids, int* tok_pos, const int* chosen, i
 // y[r, c] = tanh(alpha * x[src, c]) * w[c] + b[c], value by value in float32: a norm without a
 // mean or a variance. alpha is one float32 on the device. As with RMSNorm, `parts` partial
 // products [parts][T][H] are first added into the residual row in place, in split order.
+// `xb` (or null): a bias [H] that is added into the residual row AFTER y was formed from it:
+// the bias of a product that will be accumulated onto that row later (no row gather then).
 template <typename TW, typename TO>
 __global__ void dynamic_tanh_kernel(float* __restrict__ x, const float* __restrict__ partial,
                                     int parts, size_t part_stride, const TW* __restrict__ w,
                                     const TW* __restrict__ b, const float* __restrict__ alpha,
-                                    TO* __restrict__ y, const int* __restrict__ rows, int H) {
+                                    TO* __restrict__ y, const int* __restrict__ rows, int H,
+                                    const TW* __restrict__ xb) {
   mb_grid_wait();
   mb_grid_launch_next();
   const int r = blockIdx.x;
@@ -316,22 +319,25 @@ __global__ void dynamic_tanh_kernel(float* __restrict__ x, const float* __restri
     float v = xr[c];
     if (parts > 0) {
       for (int p = 0; p < parts; ++p) v += partial[p * part_stride + (size_t)src * H + c];
-      xr[c] = v;
+      if (!xb) xr[c] = v;
     }
+    if (xb) xr[c] = v + to_f32<TW>(xb[c]);
     yr[c] = from_f32<TO>(fmaf(tanhf(a * v), to_f32<TW>(w[c]), to_f32<TW>(b[c])));
   }
 }
 
 MB_EXPORT int mb_dynamic_tanh(float* x, const float* partial, int parts, long long part_stride,
                               const void* w, const void* b, int w_dtype, const float* alpha,
-                              void* y, int y_dtype, const int* rows, int R, int H, void* stream) {
+                              void* y, int y_dtype, const int* rows, int R, int H, const void* xb,
+                              void* stream) {
   if (R <= 0) return 0;
-  if (parts > 0 && rows) MB_FAIL("mb_dynamic_tanh: partial sums with a row gather");
+  if ((parts > 0 || xb) && rows) MB_FAIL("mb_dynamic_tanh: sums into the residual with a row gather");
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
 #define GO(TW_, TO_)                                                                          \
   mb_launch(dynamic_tanh_kernel<TW_, TO_>, dim3(R), dim3(threads), 0, s, x, partial, parts,   \
-            (size_t)part_stride, (const TW_*)w, (const TW_*)b, alpha, (TO_*)y, rows, H)
+            (size_t)part_stride, (const TW_*)w, (const TW_*)b, alpha, (TO_*)y, rows, H,        \
+            (const TW_*)xb)
   if (w_dtype == MB_F32 && y_dtype == MB_F32) GO(float, float);
   else if (w_dtype == MB_F32) GO(float, __nv_bfloat16);
   else if (y_dtype == MB_F32) GO(__nv_bfloat16, float);
@@ -390,6 +396,23 @@ MB_EXPORT int mb_gated_act(const void* in, void* out, int dtype, int T, int I, i
   }
 #undef GO
   MB_CHECK_LAUNCH("mb_gated_act");
+}
+
+// ------------------------------------------------------------------ a bias into the residual
+template <typename TW>
+__global__ void add_bias_kernel(float* __restrict__ x, const TW* __restrict__ b, int H) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  float* xr = x + (size_t)blockIdx.x * H;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) xr[c] += to_f32<TW>(b[c]);
+}
+
+MB_EXPORT int mb_add_bias(float* x, const void* b, int b_dtype, int T, int H, void* stream) {
+  if (T <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (b_dtype == MB_F32) mb_launch(add_bias_kernel<float>, dim3(T), dim3(256), 0, s, x, (const float*)b, H);
+  else mb_launch(add_bias_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, s, x, (const __nv_bfloat16*)b, H);
+  MB_CHECK_LAUNCH("mb_add_bias");
 }
 
 // ------------------------------------------------------------------ a constant factor

@@ -37,7 +37,11 @@ MB_EXPORT int mb_gemm_tc_last_splits() { return g_last_splits; }
 // kernels that the last mb_gemm_tc of this thread launched (2 when K was split)
 MB_EXPORT int mb_gemm_tc_last_launches() { return g_last_launches; }
 
-enum { TC_STORE = 0, TC_ADD = 1, TC_PARTIAL = 2, TC_SWIGLU = 3 };
+// TC_SWIGLU and TC_GEGLU: the weight's rows alternate gate and up and the output is
+// act(gate) * up with act = SiLU or the tanh form of GELU. In these two modes nothing is split,
+// and the pointer that otherwise names the partial sums may name bfloat16 biases instead, one
+// per weight row (gate and up alternating like the rows), which are added before the activation.
+enum { TC_STORE = 0, TC_ADD = 1, TC_PARTIAL = 2, TC_SWIGLU = 3, TC_GEGLU = 4 };
 
 #define TC_BM 128
 #define TC_BK 64
@@ -66,6 +70,17 @@ __device__ __forceinline__ void store_out(void* C, int c_dtype, size_t idx, floa
 __device__ __forceinline__ float silu_mul(float g, float u) {
   return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
+// the same for either activation; gelu_tanh(g) = g * sigmoid(2 sqrt(2/pi) (g + 0.044715 g^3))
+__device__ __forceinline__ float gated_mul(float g, float u, int mode) {
+  if (mode == TC_GEGLU) {
+    const float z = 1.5957691216057308f * (g + 0.044715f * g * g * g);
+    return __fdividef(g, 1.0f + __expf(-z)) * u;
+  }
+  return silu_mul(g, u);
+}
+__device__ __forceinline__ float pair_bias(const float* part, int row) {
+  return part ? __bfloat162float(((const __nv_bfloat16*)part)[row]) : 0.f;
+}
 
 // Sixteen neighbouring columns b0 .. b0 + 15 of accumulator row `a` in the prefill form
 // (tokens on the lanes): store, add into the residual, leave as a partial sum, or SwiGLU.
@@ -73,19 +88,22 @@ __device__ __forceinline__ void store_row16(const float* v, void* C, int c_dtype
                                             int a, int b0, int rowsB, int mode, float* part,
                                             long long partial_ld, long long partial_stride) {
   const bool whole = b0 + 16 <= rowsB;
-  if (mode == TC_SWIGLU) {
+  if (mode >= TC_SWIGLU) {
     // columns 2i and 2i+1 are gate and up of output feature (b0 + 2i) / 2
     __nv_bfloat16* p = (__nv_bfloat16*)C + (size_t)a * ldc + (b0 >> 1);
+    float w[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) w[j] = v[j] + (b0 + j < rowsB ? pair_bias(part, b0 + j) : 0.f);
     if (whole && (ldc & 7) == 0 && ((uintptr_t)C & 15) == 0) {
       __nv_bfloat162 h[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j)
-        h[j] = __floats2bfloat162_rn(silu_mul(v[4 * j], v[4 * j + 1]),
-                                     silu_mul(v[4 * j + 2], v[4 * j + 3]));
+        h[j] = __floats2bfloat162_rn(gated_mul(w[4 * j], w[4 * j + 1], mode),
+                                     gated_mul(w[4 * j + 2], w[4 * j + 3], mode));
       *(uint4*)p = *(uint4*)&h[0];
     } else {
       for (int j = 0; j < 16 && b0 + j + 1 < rowsB; j += 2)
-        p[j >> 1] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
+        p[j >> 1] = __float2bfloat16_rn(gated_mul(w[j], w[j + 1], mode));
     }
   } else if (mode == TC_PARTIAL) {
     float* p = part + (size_t)a * partial_ld + b0;
@@ -130,7 +148,7 @@ __device__ __forceinline__ void staged_rows(uint32_t taddr, uint32_t stage_w, in
                                             int n0, int width, int M, int N, void* C, int c_dtype,
                                             long long ldc, int mode, float* part,
                                             long long partial_ld) {
-  const int acc_cols = mode == TC_SWIGLU ? 128 : (c_dtype == MB_BF16 && mode == TC_STORE ? 64 : 32);
+  const int acc_cols = mode >= TC_SWIGLU ? 128 : (c_dtype == MB_BF16 && mode == TC_STORE ? 64 : 32);
   const uint32_t mine = stage_w + lane * 128;
 #pragma unroll 1
   for (int c0 = 0; c0 < width; c0 += acc_cols) {
@@ -140,12 +158,19 @@ __device__ __forceinline__ void staged_rows(uint32_t taddr, uint32_t stage_w, in
     for (int g = 0; g * 16 < ncols; ++g) {
       float v[16];
       tmem_ld16(taddr + c0 + 16 * g, v);
-      if (mode == TC_SWIGLU) {
+      if (mode >= TC_SWIGLU) {
+        if (part) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int col = n0 + c0 + 16 * g + j;
+            if (col < N) v[j] += pair_bias(part, col);
+          }
+        }
         __nv_bfloat162 h[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          h[j] = __floats2bfloat162_rn(silu_mul(v[4 * j], v[4 * j + 1]),
-                                       silu_mul(v[4 * j + 2], v[4 * j + 3]));
+          h[j] = __floats2bfloat162_rn(gated_mul(v[4 * j], v[4 * j + 1], mode),
+                                       gated_mul(v[4 * j + 2], v[4 * j + 3], mode));
         st_shared_v4(mine + ((g ^ (lane & 7)) << 4), *(uint4*)&h[0]);
       } else if (acc_cols == 64) {
         __nv_bfloat162 h[8];
@@ -164,7 +189,7 @@ __device__ __forceinline__ void staged_rows(uint32_t taddr, uint32_t stage_w, in
     __syncwarp();
     const int pc = lane & 7;
     // bytes of output per accumulator column: 1 (SwiGLU), 2 (bfloat16), 4 (float32)
-    const int pieces = mode == TC_SWIGLU ? ncols >> 4 : (acc_cols == 64 ? ncols >> 3 : ncols >> 2);
+    const int pieces = mode >= TC_SWIGLU ? ncols >> 4 : (acc_cols == 64 ? ncols >> 3 : ncols >> 2);
     if (acc_cols == 32) {
       float* dst = mode == TC_PARTIAL ? part : (float*)C;
       const long long ld = mode == TC_PARTIAL ? partial_ld : ldc;
@@ -189,7 +214,7 @@ __device__ __forceinline__ void staged_rows(uint32_t taddr, uint32_t stage_w, in
         }
       }
     } else {
-      const int col = (mode == TC_SWIGLU ? (n0 + c0) >> 1 : n0 + c0) + 8 * pc;
+      const int col = (mode >= TC_SWIGLU ? (n0 + c0) >> 1 : n0 + c0) + 8 * pc;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int r = 4 * i + (lane >> 3);
@@ -236,8 +261,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // adds their 16 KB); whole 16-byte pieces of output need a width, a row stride and a base
   // that are multiples of 16 bytes
   const uint32_t stage_w = bars + 1024 + (warp & 3) * 4096;
-  const int out_cols = mode == TC_SWIGLU ? rowsB >> 1 : rowsB;
-  const int per16 = (mode == TC_SWIGLU || (mode == TC_STORE && c_dtype == MB_BF16)) ? 8 : 4;
+  const int out_cols = mode >= TC_SWIGLU ? rowsB >> 1 : rowsB;
+  const int per16 = (mode >= TC_SWIGLU || (mode == TC_STORE && c_dtype == MB_BF16)) ? 8 : 4;
   const bool staged = !SWAP && out_cols % per16 == 0 &&
                       (mode == TC_PARTIAL ? (partial_ld % 4 == 0 && partial_stride % 4 == 0 &&
                                              ((uintptr_t)partial & 15) == 0)
@@ -361,15 +386,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (n0 + c0 >= rowsB) break;  // uniform over the warp
         float v[16];
         tmem_ld16(taddr + c0, v);
-        if (SWAP && mode == TC_SWIGLU) {
+        if (SWAP && mode >= TC_SWIGLU) {
           // lanes 2i and 2i+1 hold gate and up of output feature (m0 + lane_row) / 2
+          const float bias = mine ? pair_bias(part, a) : 0.f;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float up = __shfl_xor_sync(0xffffffffu, v[j], 1);
+            const float own = v[j] + bias;
+            const float up = __shfl_xor_sync(0xffffffffu, own, 1);
             const int bb = n0 + c0 + j;
             if (mine && !(lane & 1) && bb < rowsB)
               ((__nv_bfloat16*)C)[(size_t)bb * ldc + (a >> 1)] =
-                  __float2bfloat16_rn(silu_mul(v[j], up));
+                  __float2bfloat16_rn(gated_mul(own, up, mode));
           }
           continue;
         }
@@ -467,8 +494,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // the epilogue warps' staging rows lie behind the barriers; whole 16-byte pieces of output
   // need a width, a row stride and a base that are multiples of 16 bytes
   const uint32_t stage_w = bars + 1024 + (warp & 3) * 4096;
-  const int out_cols = mode == TC_SWIGLU ? N >> 1 : N;
-  const int per16 = (mode == TC_SWIGLU || (mode == TC_STORE && c_dtype == MB_BF16)) ? 8 : 4;
+  const int out_cols = mode >= TC_SWIGLU ? N >> 1 : N;
+  const int per16 = (mode >= TC_SWIGLU || (mode == TC_STORE && c_dtype == MB_BF16)) ? 8 : 4;
   const bool staged = out_cols % per16 == 0 &&
                       (mode == TC_PARTIAL ? (partial_ld % 4 == 0 && partial_stride % 4 == 0 &&
                                              ((uintptr_t)partial & 15) == 0)
@@ -723,6 +750,9 @@ MB_EXPORT int mb_gemm_tc_supported(const void* A, int lda, const void* W, int M,
 // (1 load, 2 MMA, 3 epilogue). `sms`: the number of SMs of the device. `defer`: when K was split
 // (mb_gemm_tc_last_splits() > 1) the partial sums stay in the workspace as [splits][M][N] and C
 // is not touched: the caller's next kernel adds them up.
+// set by mb_gemm_tc_gated around its call: the biases of a gated epilogue (see the modes)
+static thread_local const void* g_pair_bias = nullptr;
+
 MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_dtype, int ldc,
                          int M, int N, int K, int epilogue, float* workspace,
                          long long workspace_floats, int defer, int* error, int sms,
@@ -730,10 +760,10 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
   g_last_splits = 1;
   if (M <= 0 || N <= 0) return 0;
   if (!mb_gemm_tc_supported(A, lda, W, M, N, K)) return -1;
-  if (epilogue != TC_STORE && epilogue != TC_ADD && epilogue != TC_SWIGLU)
+  if (epilogue != TC_STORE && epilogue != TC_ADD && epilogue != TC_SWIGLU && epilogue != TC_GEGLU)
     MB_FAIL("mb_gemm_tc: epilogue %d", epilogue);
   if (epilogue == TC_ADD && c_dtype != MB_F32) MB_FAIL("mb_gemm_tc: the residual is float32");
-  if (epilogue == TC_SWIGLU && (c_dtype != MB_BF16 || (N & 1)))
+  if (epilogue >= TC_SWIGLU && (c_dtype != MB_BF16 || (N & 1)))
     MB_FAIL("mb_gemm_tc: SwiGLU writes bfloat16 from an even number of rows (%d)", N);
   cudaStream_t s = (cudaStream_t)stream;
   const bool swap = M <= 64;
@@ -761,7 +791,7 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     p.tile_rows = rows;
     p.max_ctas = slots;
     plan_stages(p, bn, 110 * 1024);
-    if (workspace && epilogue != TC_SWIGLU && tiles128 <= sms && nkb >= 8) {
+    if (workspace && epilogue < TC_SWIGLU && tiles128 <= sms && nkb >= 8) {
       int want = slots / tiles128;
       if (want > TC_MAX_SPLITS) want = TC_MAX_SPLITS;  // what the consumer adds up in one round of loads
       if (want > nkb / 4) want = nkb / 4;
@@ -777,7 +807,7 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     plan_stages(p, bn, 200 * 1024);
     p.smem += 4 * 4096;  // the epilogue warps' staging rows
     const int tiles = ((rowsA + TC_BM - 1) / TC_BM) * ((rowsB + bn - 1) / bn);
-    if (workspace && epilogue != TC_SWIGLU && tiles < sms && nkb >= 8) {
+    if (workspace && epilogue < TC_SWIGLU && tiles < sms && nkb >= 8) {
       int want = (2 * sms + tiles - 1) / tiles;
       if (want > nkb / 4) want = nkb / 4;
       const long long per = (long long)M * N;
@@ -796,7 +826,7 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     const int tiles_n = (N + bn - 1) / bn;
     const int tiles = tiles_m * tiles_n;
     p.splits = 1;
-    if (workspace && epilogue != TC_SWIGLU && tiles < pairs && nkb >= 8) {
+    if (workspace && epilogue < TC_SWIGLU && tiles < pairs && nkb >= 8) {
       int want = (2 * pairs + tiles - 1) / tiles;
       if (want > nkb / 4) want = nkb / 4;
       const long long per = (long long)M * N;
@@ -809,7 +839,7 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     if (!mb_make_map_bf16(&tmA, A, M, K, lda, 128, "mb_gemm_tc input")) return -1;
     if (!mb_make_map_bf16(&tmB, W, N, K, K, bn / 2, "mb_gemm_tc weight")) return -1;
     const int mode = p.splits > 1 ? TC_PARTIAL : epilogue;
-    float* partial = p.splits > 1 ? workspace : nullptr;
+    float* partial = p.splits > 1 ? workspace : (float*)g_pair_bias;
     int rc = 0;
     switch (bn) {
 #define PAIR(W_)                                                                                \
@@ -843,7 +873,7 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     if (!mb_make_map_bf16(&tmB, W, N, K, K, bn, "mb_gemm_tc weight")) return -1;
   }
   const int mode = p.splits > 1 ? TC_PARTIAL : epilogue;
-  float* partial = p.splits > 1 ? workspace : nullptr;
+  float* partial = p.splits > 1 ? workspace : (float*)g_pair_bias;
   const long long pstride = (long long)M * N, pld = N;
   int rc;
 #define GO(BN_, SW_)                                                                        \
@@ -866,6 +896,20 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     MB_CHECK_LAUNCH("mb_gemm_tc reduce");
   }
   return 0;
+}
+
+// C[M, N / 2] = act(gate + b_gate) * (up + b_up) for a weight [N, K] whose rows alternate gate
+// and up; act 0: SiLU, 1: the tanh form of GELU; pair_bias: bfloat16 [N], alternating like the
+// rows, or null. C is bfloat16.
+MB_EXPORT int mb_gemm_tc_gated(const void* A, int lda, const void* W, void* C, int ldc, int M,
+                               int N, int K, int act, const void* pair_bias, int* error, int sms,
+                               void* stream) {
+  if (act != 0 && act != 1) MB_FAIL("mb_gemm_tc_gated: activation %d", act);
+  g_pair_bias = pair_bias;
+  const int rc = mb_gemm_tc(A, lda, W, C, MB_BF16, ldc, M, N, K, act == 1 ? TC_GEGLU : TC_SWIGLU,
+                            nullptr, 0, 0, error, sms, stream);
+  g_pair_bias = nullptr;
+  return rc;
 }
 
 // ------------------------------------------------------------------ the bounded wait, by itself

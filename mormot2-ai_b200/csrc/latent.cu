@@ -216,9 +216,9 @@ heads_gemm_kernel(const T* __restrict__ A, int lda, int lda_h, const TB* __restr
 }
 
 // The same product on the tensor cores for bfloat16 operands (mma_tile.cuh): a block computes
-// 64 tokens x 64 outputs of one head. The gate and the rotated tail as above (the tail is
+// 128 tokens x 128 outputs of one head. The gate and the rotated tail as above (the tail is
 // read from global memory, value and partner).
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(MT_THREADS)
 heads_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, int lda_h,
                       const __nv_bfloat16* __restrict__ B, __nv_bfloat16* __restrict__ C, int ldc,
                       int ldc_h, int M, int N, int K, const __nv_bfloat16* __restrict__ gate,
@@ -227,6 +227,7 @@ heads_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, int lda_h,
   mb_grid_wait();
   mb_grid_launch_next();
   __shared__ __align__(16) MtShared<1> sh;
+  constexpr int MT_BN = 128;
   const int h = blockIdx.z, m0 = blockIdx.y * MT_BM, n0 = blockIdx.x * MT_BN;
   const __nv_bfloat16* Ah = A + (size_t)h * lda_h;
   if (threadIdx.x < MT_BM) {
@@ -235,9 +236,9 @@ heads_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, int lda_h,
   }
   __syncthreads();
   const __nv_bfloat16* b[1] = {B + ((size_t)h * N + n0) * K};
-  float acc[1][2][4][4];
+  float acc[1][2][8][4];
   mt_mainloop<1>(sh, b, min(MT_BN, N - n0), K, acc);
-  mt_for_each([&](int r, int c, int mi, int ni, int e) {
+  mt_for_each<1>([&](int r, int c, int mi, int ni, int e) {
     const int gm = m0 + r, gn = n0 + c;
     if (gm >= M || gn >= N) return;
     float v = acc[0][mi][ni][e];
@@ -284,8 +285,8 @@ MB_EXPORT int mb_heads_gemm(const void* A, int dtype, int lda, int lda_h, const 
   // weight once with a sixteenth of the multiply-adds of a 64-row tile)
   if (dtype == MB_BF16 && b_dtype == MB_BF16 && M > 16 && K % 8 == 0 && lda % 8 == 0 &&
       lda_h % 8 == 0 && (((uintptr_t)A | (uintptr_t)B) & 15) == 0) {
-    mb_launch(heads_gemm_mma_kernel, dim3((N + MT_BN - 1) / MT_BN, (M + MT_BM - 1) / MT_BM, heads),
-              dim3(128), 0, s, (const __nv_bfloat16*)A, lda, lda_h, (const __nv_bfloat16*)B,
+    mb_launch(heads_gemm_mma_kernel, dim3((N + 127) / 128, (M + MT_BM - 1) / MT_BM, heads),
+              dim3(MT_THREADS), 0, s, (const __nv_bfloat16*)A, lda, lda_h, (const __nv_bfloat16*)B,
               (__nv_bfloat16*)C, ldc, ldc_h, M, N, K, (const __nv_bfloat16*)gate, ldg, tail,
               rot_dims, inv_freq, amplitude, tok_pos);
     MB_CHECK_LAUNCH("mb_heads_gemm");

@@ -15,7 +15,8 @@
 // bfloat16, and then each adds P · V for its half of the kv_rank output columns (V = the same
 // tile, read with ldmatrix.trans), with the output rows in registers (kv_rank / 4 floats a
 // thread). A decode step of few sequences deals the key tiles of a sequence out over `splits`
-// blocks that leave (max, sum, unnormalised output) in float32 scratch for a merge kernel.
+// blocks that leave (max, sum, unnormalised output) in float32 scratch; the block that
+// finishes last (a ticket counter, no waiting) adds them up.
 //
 // Sizes: dk and kv_rank multiples of 16, kv_rank at most 512; other sizes use the kernel of
 // latent.cu. There is no wait on another block or on a barrier object, so nothing can hang.
@@ -41,6 +42,13 @@ __device__ __forceinline__ void lm_ldmatrix_x4_trans(uint32_t (&r)[4], const voi
                : "r"(s));
 }
 
+__device__ __forceinline__ void lm_ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s));
+}
+
 // NV: the most n8 tiles of output columns a warp holds (kv_rank / 16 of them are used).
 template <int NV>
 __global__ void __launch_bounds__(LM_THREADS, 1)
@@ -50,7 +58,8 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                             const int* __restrict__ page_table, int max_pages, int ring_pages,
                             const int* __restrict__ seq_start, const int* __restrict__ seq_past,
                             const int* __restrict__ seq_slot, int B, int nh, int kv_rank, int dk,
-                            int window, float scale, int splits, float* __restrict__ scratch) {
+                            int window, float scale, int splits, float* __restrict__ scratch,
+                            unsigned int* __restrict__ tickets) {
   mb_grid_wait();
   mb_grid_launch_next();
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -94,16 +103,16 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
   if (window > 0) key_lo = max(0, past + tok_lo + 1 - window);
   const int tile_lo = key_lo / LM_KEYS, n_tiles = key_hi / LM_KEYS + 1 - tile_lo;
 
+  // eight threads bring one key's row: a thread looks its key's page up once a tile and then
+  // copies every eighth 16-byte piece of the row
+  const int my_key = tid >> 3, my_piece = tid & 7;
   auto load_keys = [&](int stage, int j) {
-    const int k0 = (tile_lo + j) * LM_KEYS;
-    __nv_bfloat16* dst = ks + stage * LM_KEYS * pitch;
-    for (int c = tid; c < LM_KEYS * chunks; c += LM_THREADS) {
-      const int r = c / chunks, kc = (c - r * chunks) * 8;
-      const int key = k0 + r;
-      const bool ok = key <= key_hi;
-      const size_t row = ok ? kv_row(page_table, max_pages, ring_pages, slot, key, 1, 0) : 0;
-      lm_cp16(dst + r * pitch + kc, pool + row * dk + kc, ok);
-    }
+    const int key = (tile_lo + j) * LM_KEYS + my_key;
+    const bool ok = key <= key_hi;
+    const size_t row = ok ? kv_row(page_table, max_pages, ring_pages, slot, key, 1, 0) : 0;
+    const __nv_bfloat16* src = pool + row * dk;
+    __nv_bfloat16* dst = ks + (stage * LM_KEYS + my_key) * pitch;
+    for (int kc = my_piece * 8; kc < dk; kc += 64) lm_cp16(dst + kc, src + kc, ok);
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
 
@@ -131,18 +140,41 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     float s[2][4];
 #pragma unroll
     for (int ni = 0; ni < 2; ++ni) s[ni][0] = s[ni][1] = s[ni][2] = s[ni][3] = 0.f;
-    const __nv_bfloat16* qa = qs + (16 * rg + g) * pitch + 2 * t;
-    const __nv_bfloat16* kb = kt + (16 * cs + g) * pitch + 2 * t;
-    for (int k = 0; k < dk; k += 16) {
-      const uint32_t a0 = *(const uint32_t*)(qa + k), a1 = *(const uint32_t*)(qa + 8 * pitch + k);
-      const uint32_t a2 = *(const uint32_t*)(qa + k + 8);
-      const uint32_t a3 = *(const uint32_t*)(qa + 8 * pitch + k + 8);
+    // four 8 x 8 pieces with one instruction each: of Q rows 0-7 / 8-15 x values k.. / k+8..
+    // (the A operand), of K keys 0-7 x values k.. / k+8.., keys 8-15 x the same (the B
+    // operands of the warp's two groups of eight keys)
+    const __nv_bfloat16* qa = qs + (16 * rg + (lane & 15)) * pitch + (lane >> 4) * 8;
+    const __nv_bfloat16* kb = kt + (16 * cs + (lane & 7) + ((lane >> 4) << 3)) * pitch +
+                              ((lane >> 3) & 1) * 8;
+    // two k steps at a time into accumulators of their own: four independent chains of
+    // products instead of two (a chain's next product waits for the one before)
+    float s2[2][4];
 #pragma unroll
-      for (int ni = 0; ni < 2; ++ni) {
-        const __nv_bfloat16* p = kb + 8 * ni * pitch + k;
-        mma_bf16(s[ni], a0, a1, a2, a3, *(const uint32_t*)p, *(const uint32_t*)(p + 8));
-      }
+    for (int ni = 0; ni < 2; ++ni) s2[ni][0] = s2[ni][1] = s2[ni][2] = s2[ni][3] = 0.f;
+    int k = 0;
+#pragma unroll 2
+    for (; k + 32 <= dk; k += 32) {
+      uint32_t a[4], bq[4], a2[4], bq2[4];
+      lm_ldmatrix_x4(a, qa + k);
+      lm_ldmatrix_x4(bq, kb + k);
+      lm_ldmatrix_x4(a2, qa + k + 16);
+      lm_ldmatrix_x4(bq2, kb + k + 16);
+      mma_bf16(s[0], a[0], a[1], a[2], a[3], bq[0], bq[1]);
+      mma_bf16(s[1], a[0], a[1], a[2], a[3], bq[2], bq[3]);
+      mma_bf16(s2[0], a2[0], a2[1], a2[2], a2[3], bq2[0], bq2[1]);
+      mma_bf16(s2[1], a2[0], a2[1], a2[2], a2[3], bq2[2], bq2[3]);
     }
+    if (k < dk) {
+      uint32_t a[4], bq[4];
+      lm_ldmatrix_x4(a, qa + k);
+      lm_ldmatrix_x4(bq, kb + k);
+      mma_bf16(s[0], a[0], a[1], a[2], a[3], bq[0], bq[1]);
+      mma_bf16(s[1], a[0], a[1], a[2], a[3], bq[2], bq[3]);
+    }
+#pragma unroll
+    for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[ni][e] += s2[ni][e];
     // ---- scale, mask, the rows' maxima over this warp's keys
     const int key0 = (tile_lo + j) * LM_KEYS + 16 * cs + 2 * t;
     float mt[2] = {-INFINITY, -INFINITY};
@@ -257,52 +289,85 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         }
     }
   }
-}
-
-// out[row, :] = sum_s exp(m_s - M) O_s / sum_s exp(m_s - M) l_s over the splits of a row
-// (scratch [rows][splits][2 + kv_rank]: max, sum, unnormalised output).
-__global__ void latent_merge_kernel(const float* __restrict__ scratch, int splits, int kv_rank,
-                                    int nh, __nv_bfloat16* __restrict__ out, int out_stride) {
-  mb_grid_wait();
-  mb_grid_launch_next();
-  const int row = blockIdx.x;
-  const float* src = scratch + (size_t)row * splits * (kv_rank + 2);
-  float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, src[(size_t)s * (kv_rank + 2)]);
-  float l = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float m = src[(size_t)s * (kv_rank + 2)];
-    if (m != -INFINITY) l += expf(m - M) * src[(size_t)s * (kv_rank + 2) + 1];
-  }
-  const float inv = 1.0f / l;
-  __nv_bfloat16* dst = out + (size_t)(row / nh) * out_stride + (size_t)(row % nh) * kv_rank;
-  for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) {
-    float v = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float m = src[(size_t)s * (kv_rank + 2)];
-      if (m != -INFINITY) v = fmaf(expf(m - M), src[(size_t)s * (kv_rank + 2) + 2 + c], v);
+  if (splits == 1) return;
+  // ---- the block that finishes last of a tile's splits adds them up: out[row] =
+  // sum_s exp(m_s - M) O_s / sum_s exp(m_s - M) l_s. The ticket counter wraps to 0 by itself,
+  // so the next launch finds it as this one did; nobody waits for anybody.
+  __shared__ unsigned int ticket;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) ticket = atomicInc(&tickets[blockIdx.x], (unsigned)splits - 1);
+  __syncthreads();
+  if (ticket != (unsigned)splits - 1) return;
+  __threadfence();
+  const int width = kv_rank + 2;
+  // every row's weights exp(m_s - M) / sum first (a thread a row), then all threads add the
+  // splits' outputs up, a pair of columns each, with the splits' loads in flight together
+  float* wts = (float*)ks;                                   // [64][16]
+  const int rows_here = min(LM_ROWS, n_new * nh - row0);
+  if (tid < rows_here) {
+    const int row = row0 + tid;
+    const float* src = scratch + ((size_t)first * nh + row) * splits * width;
+    float m[16], l[16], M = -INFINITY;
+#pragma unroll
+    for (int sp = 0; sp < 16; ++sp) {
+      m[sp] = sp < splits ? __ldcg(src + (size_t)sp * width) : -INFINITY;
+      l[sp] = sp < splits ? __ldcg(src + (size_t)sp * width + 1) : 0.f;
+      M = fmaxf(M, m[sp]);
     }
-    dst[c] = __float2bfloat16_rn(v * inv);
+    float total = 0.f;
+#pragma unroll
+    for (int sp = 0; sp < 16; ++sp) {
+      m[sp] = m[sp] == -INFINITY ? 0.f : expf(m[sp] - M);
+      total = fmaf(m[sp], l[sp], total);
+    }
+    const float inv = 1.0f / total;
+#pragma unroll
+    for (int sp = 0; sp < 16; ++sp) wts[tid * 16 + sp] = m[sp] * inv;
+  }
+  __syncthreads();
+  const int pairs = kv_rank / 2;
+  for (int e = tid; e < rows_here * pairs; e += LM_THREADS) {
+    const int r = e / pairs, c = 2 * (e - r * pairs);
+    const int row = row0 + r;
+    const float* src = scratch + ((size_t)first * nh + row) * splits * width + 2 + c;
+    float2 part[16];
+#pragma unroll
+    for (int sp = 0; sp < 16; ++sp)
+      part[sp] = sp < splits ? __ldcg((const float2*)(src + (size_t)sp * width))
+                             : make_float2(0.f, 0.f);
+    float v0 = 0.f, v1 = 0.f;
+#pragma unroll
+    for (int sp = 0; sp < 16; ++sp) {
+      const float w = wts[r * 16 + sp];
+      v0 = fmaf(w, part[sp].x, v0);
+      v1 = fmaf(w, part[sp].y, v1);
+    }
+    const int tok = row / nh, head = row - tok * nh;
+    *(uint32_t*)(out + (size_t)(first + tok) * out_stride + (size_t)head * kv_rank + c) =
+        pack_bf16(v0, v1);
   }
 }
 
 // q [T, nh * dk] (row stride q_stride), out [T, nh * kv_rank]; `tiles` = the sum over the
 // step's sequences of ceil(new tokens * nh / 64), as the host counts it; `splits` > 1 needs
-// scratch of T * nh * splits * (kv_rank + 2) floats.
+// scratch of T * nh * splits * (kv_rank + 2) floats and `tickets`, `tiles` counters that are 0
+// (the kernel leaves them 0).
 MB_EXPORT int mb_latent_attention_mma(const void* q, int q_stride, void* out, int out_stride,
                                       const void* pool, const int* page_table, int max_pages,
                                       int ring_pages, const int* seq_start, const int* seq_past,
                                       const int* seq_slot, int B, int T, int tiles, int nh,
                                       int kv_rank, int rot_dim, int window, float scale,
                                       int splits, float* scratch, long long scratch_floats,
-                                      void* stream) {
+                                      unsigned int* tickets, void* stream) {
   if (T <= 0 || tiles <= 0) return 0;
   const int dk = kv_rank + rot_dim;
   if (dk % 16 || kv_rank % 16 || kv_rank > 512 || q_stride % 8 || out_stride % 2 ||
       (((uintptr_t)q | (uintptr_t)pool) & 15) || ((uintptr_t)out & 3))
     MB_FAIL("mb_latent_attention_mma: sizes %d + %d or alignment not supported", kv_rank, rot_dim);
   if (splits < 1) splits = 1;
-  if (splits > 1 && (scratch == nullptr ||
+  if (splits > 16) MB_FAIL("mb_latent_attention_mma: at most 16 splits, not %d", splits);
+  if (splits > 1 && (scratch == nullptr || tickets == nullptr ||
                      (long long)T * nh * splits * (kv_rank + 2) > scratch_floats))
     MB_FAIL("mb_latent_attention_mma: scratch for %d splits", splits);
   cudaStream_t s = (cudaStream_t)stream;
@@ -322,16 +387,10 @@ MB_EXPORT int mb_latent_attention_mma(const void* q, int q_stride, void* out, in
     mb_launch(latent_attention_mma_kernel<NV_>, grid, dim3(LM_THREADS), smem, s,              \
               (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,             \
               (const __nv_bfloat16*)pool, page_table, max_pages, ring_pages, seq_start,       \
-              seq_past, seq_slot, B, nh, kv_rank, dk, window, scale, splits, scratch);        \
+              seq_past, seq_slot, B, nh, kv_rank, dk, window, scale, splits, scratch,         \
+              tickets);                                                                       \
   }
   if (kv_rank <= 128) GO(8) else if (kv_rank <= 256) GO(16) else GO(32)
 #undef GO
-  {
-    cudaError_t e_ = cudaGetLastError();
-    if (e_ != cudaSuccess) MB_FAIL("mb_latent_attention_mma: %s", cudaGetErrorString(e_));
-  }
-  if (splits > 1)
-    mb_launch(latent_merge_kernel, dim3(T * nh), dim3(128), 0, s, (const float*)scratch, splits,
-              kv_rank, nh, (__nv_bfloat16*)out, out_stride);
   MB_CHECK_LAUNCH("mb_latent_attention_mma");
 }

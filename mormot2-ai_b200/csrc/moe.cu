@@ -237,10 +237,10 @@ moe_gemm_kernel(const T* __restrict__ in, const TW* __restrict__ W, void* __rest
 }
 
 // The same two products on the tensor cores for bfloat16 operands (mma_tile.cuh); the plan's
-// tiles have 64 rows. The first product multiplies the gathered rows with the gate and the up
+// tiles have 128 rows. The first product multiplies the gathered rows with the gate and the up
 // rows of the expert at once.
 template <bool UP>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(MT_THREADS)
 moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ W,
                     void* __restrict__ out, const int* __restrict__ plan, int A, int E,
                     int max_tiles, int top, int N, int K, int act,
@@ -248,6 +248,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* _
   mb_grid_wait();
   mb_grid_launch_next();
   constexpr int NB = UP ? 2 : 1;
+  constexpr int MT_BN = 128 / NB;
   const int tile = blockIdx.y;
   if (tile >= plan[0]) return;
   const int* offsets = plan + 1;
@@ -269,9 +270,9 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* _
   const __nv_bfloat16* b[NB];
 #pragma unroll
   for (int nb = 0; nb < NB; ++nb) b[nb] = We + ((size_t)nb * N + n0) * K;
-  float acc[NB][2][4][4];
+  float acc[NB][2][8 / NB][4];
   mt_mainloop<NB>(sh, b, min(MT_BN, N - n0), K, acc);
-  mt_for_each([&](int r, int c, int mi, int ni, int el) {
+  mt_for_each<NB>([&](int r, int c, int mi, int ni, int el) {
     const int gn = n0 + c;
     if (r >= rows || gn >= N) return;
     if (UP) {
@@ -288,18 +289,22 @@ MB_EXPORT int mb_moe_gemm(const void* in, int dtype, const void* W, int w_dtype,
                           const int* plan, int A, int E, int max_tiles, int bm, int top, int N,
                           int K, int up, int act, const float* weight, void* stream) {
   if (A <= 0) return 0;
-  if (bm != 16 && bm != 64) MB_FAIL("mb_moe_gemm: tiles of %d rows", bm);
+  if (bm != 16 && bm != 64 && bm != 128) MB_FAIL("mb_moe_gemm: tiles of %d rows", bm);
   if (!up && weight == nullptr) MB_FAIL("mb_moe_gemm: the second product needs the weights");
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid((N + MG_BN - 1) / MG_BN, max_tiles);
-  if (dtype == MB_BF16 && w_dtype == MB_BF16 && bm == 64 && K % 8 == 0 &&
-      (((uintptr_t)in | (uintptr_t)W) & 15) == 0) {
+  if (bm == 128) {
+    if (!(dtype == MB_BF16 && w_dtype == MB_BF16 && K % 8 == 0 &&
+          (((uintptr_t)in | (uintptr_t)W) & 15) == 0))
+      MB_FAIL("mb_moe_gemm: tiles of 128 rows are the tensor-core kernel's (bfloat16, K %% 8 == 0)");
     if (up)
-      mb_launch(moe_gemm_mma_kernel<true>, grid, dim3(128), 0, s, (const __nv_bfloat16*)in,
-                (const __nv_bfloat16*)W, out, plan, A, E, max_tiles, top, N, K, act, weight);
+      mb_launch(moe_gemm_mma_kernel<true>, dim3((N + 63) / 64, max_tiles), dim3(MT_THREADS), 0, s,
+                (const __nv_bfloat16*)in, (const __nv_bfloat16*)W, out, plan, A, E, max_tiles, top,
+                N, K, act, weight);
     else
-      mb_launch(moe_gemm_mma_kernel<false>, grid, dim3(128), 0, s, (const __nv_bfloat16*)in,
-                (const __nv_bfloat16*)W, out, plan, A, E, max_tiles, top, N, K, act, weight);
+      mb_launch(moe_gemm_mma_kernel<false>, dim3((N + 127) / 128, max_tiles), dim3(MT_THREADS), 0,
+                s, (const __nv_bfloat16*)in, (const __nv_bfloat16*)W, out, plan, A, E, max_tiles,
+                top, N, K, act, weight);
     MB_CHECK_LAUNCH("mb_moe_gemm");
   }
 #define GO(T_, TW_, BM_, UP_)                                                                \

@@ -47,6 +47,10 @@ class Runtime:
         self.attention_scratch = (alloc(guards, "attention split results", (1 << 20,),
                                         torch.float32, self.device, None)
                                   if self.fast_kernels else None)
+        # counters of kernels whose blocks take tickets (the block that finishes last of a group
+        # adds the group's partial results up); zero between launches
+        self.tickets = (alloc(guards, "tickets", (4096,), torch.int32, self.device)
+                        if self.fast_kernels else None)
         # word 0: set by a kernel when one of its bounded waits ran out; the words after it: the
         # tokens that the sampler chose in a step, so that one copy brings both to the host
         self.mailbox = alloc(guards, "mailbox", (1 + MAILBOX_TOKENS,), torch.int32, self.device)
@@ -145,8 +149,11 @@ class Runtime:
                 blocks = step.B * (-(-nh // 64))
                 room = self.attention_scratch.numel() // max(1, step.T * nh * (kv_rank + 2))
                 splits = max(1, min(self.sms // blocks, pages * (PAGE // 32), 16, room))
+                if blocks > self.tickets.numel():
+                    splits = 1
             K.latent_attention_mma(q, out, step, line, nh, kv_rank, rot_dim, window, scale,
-                                   splits, self.attention_scratch if splits > 1 else None)
+                                   splits, self.attention_scratch if splits > 1 else None,
+                                   self.tickets if splits > 1 else None)
             return
         K.latent_attention(q, out, step, line, nh, kv_rank, rot_dim, window, scale)
 

@@ -68,7 +68,8 @@ CLASS_OF = {"mb_gemm_tc": "products", "mb_gemm_simt": "products",
             "mb_qk_norm_rope_store": "rotary", "mb_embed": "embedding", "mb_swiglu": "activation",
             "mb_argmax": "sampling", "mb_sample": "sampling", "mb_sample_filtered": "sampling",
             "mb_advance_decode": "sampling", "mb_dynamic_tanh": "norms",
-            "mb_gated_act": "activation", "mb_scale": "activation", "mb_latent_prep": "rotary",
+            "mb_gated_act": "activation", "mb_scale": "activation", "mb_add_bias": "activation",
+            "mb_gemm_tc_gated": "products", "mb_latent_prep": "rotary",
             "mb_heads_gemm": "products", "mb_latent_attention": "attention",
             "mb_latent_attention_mma": "attention",
             "mb_moe_route": "routing", "mb_moe_plan": "routing", "mb_moe_gemm": "products",
@@ -254,9 +255,11 @@ ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
 
 def dynamic_tanh(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, alpha: torch.Tensor,
                  out: torch.Tensor, rows: Optional[torch.Tensor] = None,
-                 n_rows: Optional[int] = None, partial: Optional[torch.Tensor] = None) -> None:
+                 n_rows: Optional[int] = None, partial: Optional[torch.Tensor] = None,
+                 residual_bias: Optional[torch.Tensor] = None) -> None:
     """out[r] = tanh(alpha * x[rows[r] or r]) * w + b; ``alpha``: one float32 on the device.
-    ``partial`` [parts, T, H] float32 is first added into x."""
+    ``partial`` [parts, T, H] float32 is first added into x. ``residual_bias`` [H] is added
+    into x after out was formed (the bias of a product that is accumulated onto x later)."""
     H = x.shape[-1]
     R = n_rows if n_rows is not None else (rows.numel() if rows is not None else x.shape[0])
     assert x.dtype == torch.float32 and w.numel() == H and b.numel() == H
@@ -266,10 +269,20 @@ def dynamic_tanh(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, alpha: torch
     if partial is not None:
         assert partial.dtype == torch.float32 and partial.is_contiguous()
         parts, stride = partial.shape[0], partial.stride(0)
+    if residual_bias is not None:
+        assert residual_bias.dtype == w.dtype and residual_bias.numel() == H
     _call("elementwise", "mb_dynamic_tanh",
-          [_vp, _vp, _i, _ll, _vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _vp],
+          [_vp, _vp, _i, _ll, _vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _vp, _vp],
           _ptr(x), _ptr(partial), parts, stride, _ptr(w), _ptr(b), code_of(w.dtype), _ptr(alpha),
-          _ptr(out), code_of(out.dtype), _ptr(rows), R, H, _stream())
+          _ptr(out), code_of(out.dtype), _ptr(rows), R, H, _ptr(residual_bias), _stream())
+
+
+def add_bias(x: torch.Tensor, b: torch.Tensor) -> None:
+    """x[t, :] += b (x float32)."""
+    assert x.dtype == torch.float32 and b.numel() == x.shape[1]
+    _contig(x, "x")
+    _call("elementwise", "mb_add_bias", [_vp, _vp, _i, _i, _i, _vp],
+          _ptr(x), _ptr(b), code_of(b.dtype), x.shape[0], x.shape[1], _stream())
 
 
 def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: int,
@@ -360,22 +373,26 @@ def latent_attention(q: torch.Tensor, out: torch.Tensor, step, line, nh: int, kv
 
 def latent_attention_mma(q: torch.Tensor, out: torch.Tensor, step, line, nh: int, kv_rank: int,
                          rot_dim: int, window: int, scale: float, splits: int,
-                         scratch: Optional[torch.Tensor]) -> None:
+                         scratch: Optional[torch.Tensor],
+                         tickets: Optional[torch.Tensor] = None) -> None:
     """``latent_attention`` on the tensor cores (bfloat16; kv_rank and kv_rank + rot_dim
     multiples of 16, kv_rank at most 512). ``splits`` > 1: the key tiles of a sequence are
-    dealt out over that many blocks, whose partial results meet in ``scratch`` (float32)."""
+    dealt out over that many blocks, whose partial results meet in ``scratch`` (float32);
+    ``tickets``: int32 zeros, one per 64 (token, head) rows of the step, left zero."""
     T = out.shape[0]
     _contig(out, "out"), _contig(q, "q")
     assert q.dtype == out.dtype == line.k.dtype == torch.bfloat16
     tiles = sum(-(-n * nh // 64) for n in step.host_new)
+    if splits > 1:
+        assert tickets is not None and tickets.dtype == torch.int32 and tickets.numel() >= tiles
     _call("latent_mma", "mb_latent_attention_mma",
           [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i,
-           _vp, _ll, _vp],
+           _vp, _ll, _vp, _vp],
           _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.page_table),
           line.max_pages, line.ring_pages, _ptr(step.seq_start), _ptr(step.seq_past),
           _ptr(step.seq_slot), step.B, T, tiles, nh, kv_rank, rot_dim, window, float(scale),
-          splits, _ptr(scratch), scratch.numel() if scratch is not None else 0, _stream(),
-          launches=2 if splits > 1 else 1)
+          splits, _ptr(scratch), scratch.numel() if scratch is not None else 0,
+          _ptr(tickets), _stream())
 
 
 # ------------------------------------------------------------------------------ routed experts
@@ -516,6 +533,23 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, add: bool,
     lib = build.load_library("gemm_tc")
     Launches.count += lib.mb_gemm_tc_last_launches() - 1
     return lib.mb_gemm_tc_last_splits()
+
+
+def gemm_tc_gated(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, act: int,
+                  pair_bias: Optional[torch.Tensor], error: torch.Tensor, sms: int) -> None:
+    """c [M, N / 2] = act(gate + bias) * (up + bias) for a bfloat16 weight [N, K] whose rows
+    alternate gate and up (``pair_bias`` [N] bfloat16 alternates likewise, or None), in the
+    epilogue of the tensor-core product."""
+    M, Kd = a.shape
+    N = w.shape[0]
+    assert a.dtype == w.dtype == c.dtype == torch.bfloat16 and w.shape[1] == Kd
+    assert a.stride(1) == 1 and c.stride(1) == 1 and c.shape == (M, N // 2)
+    _contig(w, "the weight")
+    if pair_bias is not None:
+        assert pair_bias.dtype == torch.bfloat16 and pair_bias.numel() == N
+    _call("gemm_tc", "mb_gemm_tc_gated", [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp],
+          _ptr(a), a.stride(0), _ptr(w), _ptr(c), c.stride(0), M, N, Kd, act, _ptr(pair_bias),
+          _ptr(error), sms, _stream())
 
 
 def wait_selftest(error: torch.Tensor, code: int, tries: int = 2048) -> bool:

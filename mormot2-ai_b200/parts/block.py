@@ -27,17 +27,25 @@ class PreNormResidualBlock(Part):
         pending = self.mixer.forward(h, x, step, line, state, writes_cache)
         if "feed_forward" not in self.norms:      # a layer without a feed-forward
             return pending
+        # a feed-forward may name a bias that belongs into the residual before its last product
+        # accumulates onto it (``residual_bias``); a norm that can adds it while it has the row
+        bias = getattr(self.feed_forward, "residual_bias", None)
+        norm = self.norms["feed_forward"]
+        if bias is not None and getattr(norm, "accepts_residual_bias", False) \
+                and bias.dtype == norm.weight.dtype:
+            h = self._norm("feed_forward", x, pending, residual_bias=bias)
+            return self.feed_forward.forward(h, x, step, bias_placed=True)
         h = self._norm("feed_forward", x, pending)
         return self.feed_forward.forward(h, x, step)
 
-    def _norm(self, which, x, pending):
+    def _norm(self, which, x, pending, **more):
         norm = self.norms[which]
         if pending is None:
-            return norm.forward(x)
+            return norm.forward(x, **more)
         if getattr(norm, "accepts_pending", False):
-            return norm.forward(x, pending=pending)
+            return norm.forward(x, pending=pending, **more)
         settle(x, pending)             # a norm that knows nothing of pending sums
-        return norm.forward(x)
+        return norm.forward(x, **more)
 
 
 def settle(x, pending) -> None:

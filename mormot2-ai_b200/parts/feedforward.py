@@ -1,8 +1,12 @@
 """Feed-forwards without routing.
 
 ``gated_mlp``: x += W_d (act(W_g h + b_g) * (W_u h + b_u)) + b_d with ``activation`` "silu" or
-"gelu_tanh" and optional biases; gate and up are one product, the activation kernel adds the
-biases (and leaves b_d in the residual rows that the last product then accumulates onto).
+"gelu_tanh" and optional biases. Gate and up are one product. In bfloat16 their rows
+alternate and the product's epilogue adds the biases and applies the activation (as the
+SwiGLU feed-forward does for SiLU without biases); b_d is placed in the residual rows, which
+the last product then accumulates onto, by the norm before the feed-forward where that norm
+can (``residual_bias``), else by a kernel of its own. On the 32-bit path the product stores
+gate and up and one kernel adds the biases, applies the activation and places b_d.
 ``none``: a layer without a feed-forward.
 
 SwiGLU feed-forward: x += (silu(h·Wgᵀ) · (h·Wuᵀ)) · Wdᵀ, no bias
@@ -91,27 +95,45 @@ class GatedMlp(Part):
         g, u = weights[n["gate"]], weights[n["up"]]
         if g.dtype != u.dtype:
             g, u = g.float(), u.float()
-        self.gate_up = Linear(torch.cat([g, u], dim=0), rt)      # gate rows, then up rows
-        if getattr(rt, "consume_weights", False):
-            del g, u
-            weights.pop(n["gate"], None)
-            weights.pop(n["up"], None)
-        self.down = Linear(weights[n["down"]], rt)
         self.biases = None
         if self.bias:
             b = [weights[n["gate_bias"]], weights[n["up_bias"]], weights[n["down_bias"]]]
             if len({t.dtype for t in b}) > 1:
                 b = [t.float() for t in b]
             self.biases = b
+        # the fused form: bfloat16 weights (and biases) on the tensor-core kernel
+        self.fused = (rt.fast_kernels and g.dtype == torch.bfloat16 and self.hidden % 8 == 0
+                      and (self.biases is None or self.biases[0].dtype == torch.bfloat16))
+        if self.fused:
+            pairs = torch.stack([g, u], dim=1).reshape(2 * self.inter, self.hidden)
+            pair_bias = (torch.stack(self.biases[:2], dim=1).reshape(-1).contiguous()
+                         if self.biases is not None else None)
+            self.gate_up = Linear(pairs, rt, swiglu=True, activation=self.act, pair_bias=pair_bias)
+            self.fused = self.gate_up.fast is not None
+        if not self.fused:
+            self.gate_up = Linear(torch.cat([g, u], dim=0), rt)  # gate rows, then up rows
+        if getattr(rt, "consume_weights", False):
+            del g, u
+            weights.pop(n["gate"], None)
+            weights.pop(n["up"], None)
+        self.down = Linear(weights[n["down"]], rt)
+        # what the norm before this feed-forward may add into the residual for it
+        self.residual_bias = self.biases[2] if (self.fused and self.biases is not None) else None
 
-    def forward(self, h, x, step):
+    def forward(self, h, x, step, bias_placed: bool = False):
+        """``bias_placed``: the norm before already added ``residual_bias`` into x."""
         from .linear import Pending
-        gu = self.gate_up(h)
-        act = torch.empty((h.shape[0], self.inter), dtype=self.rt.dtype, device=h.device)
-        if self.biases is not None:
-            K.gated_act(gu, act, self.act, self.biases[0], self.biases[1], x, self.biases[2])
+        if self.fused:
+            act = self.gate_up(h)
+            if self.residual_bias is not None and not bias_placed:
+                K.add_bias(x, self.residual_bias)
         else:
-            K.gated_act(gu, act, self.act)
+            gu = self.gate_up(h)
+            act = torch.empty((h.shape[0], self.inter), dtype=self.rt.dtype, device=h.device)
+            if self.biases is not None:
+                K.gated_act(gu, act, self.act, self.biases[0], self.biases[1], x, self.biases[2])
+            else:
+                K.gated_act(gu, act, self.act)
         out = self.down(act, add_into=x, defer=True)
         return out if isinstance(out, Pending) else None
 

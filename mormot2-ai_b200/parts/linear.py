@@ -26,19 +26,26 @@ class Pending:
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor, rt, swiglu: bool = False):
+    def __init__(self, weight: torch.Tensor, rt, swiglu: bool = False, activation: int = 0,
+                 pair_bias: Optional[torch.Tensor] = None):
         """``swiglu``: the weight is [2 * out, in] with rows that alternate gate and up (row 2i
         the gate, row 2i + 1 the up projection of output i) and the product is followed by
-        out = silu(gate) * up in the kernel's epilogue."""
+        out = silu(gate) * up in the kernel's epilogue. ``activation`` (``kernels.ACT_*``)
+        other than SiLU, or ``pair_bias`` ([2 * out], alternating like the rows, added before
+        the activation): only the tensor-core kernel has that epilogue."""
         self.weight = weight.contiguous()
         self.rt = rt
         self.swiglu = swiglu
+        self.activation, self.pair_bias = activation, pair_bias
+        self.plain_swiglu = activation == K.ACT_SILU and pair_bias is None
         self.out_features = weight.shape[0] // (2 if swiglu else 1)
         self.in_features = weight.shape[1]
         self.fast = None
         if rt.fast_kernels and weight.dtype == torch.bfloat16 and rt.dtype == torch.bfloat16:
             from .linear_fast import FastLinear
             self.fast = FastLinear.maybe(self.weight, rt, swiglu)
+            if self.fast is not None and swiglu and not self.plain_swiglu:
+                self.fast.gated = (activation, pair_bias)
 
     def __call__(self, a: torch.Tensor, out: Optional[torch.Tensor] = None,
                  add_into: Optional[torch.Tensor] = None,
@@ -57,6 +64,10 @@ class Linear:
                               device=a.device)
         if self.fast is not None and self.fast(a, out, add_into):
             return add_into if add_into is not None else out
+        if self.swiglu and not self.plain_swiglu:
+            from ..errors import KernelError
+            raise KernelError("a gated epilogue with a bias or another activation than SiLU "
+                              "needs bfloat16 operands on 16-byte boundaries")
         if add_into is not None:
             K.gemm_simt(a, self.weight, add_into, K.EPI_ADD)
             return add_into

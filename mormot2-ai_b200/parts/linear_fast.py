@@ -15,6 +15,7 @@ from .. import kernels as K
 class FastLinear:
     def __init__(self, weight: torch.Tensor, rt, swiglu: bool):
         self.weight, self.rt, self.swiglu = weight, rt, swiglu
+        self.gated = None       # (activation, pair bias) of a gated epilogue that is not plain SwiGLU
 
     @classmethod
     def maybe(cls, weight: torch.Tensor, rt, swiglu: bool) -> Optional["FastLinear"]:
@@ -46,6 +47,10 @@ class FastLinear:
             return False
         rt = self.rt
         if self.swiglu:
+            if self.gated is not None:
+                K.gemm_tc_gated(a, self.weight, out, self.gated[0], self.gated[1], rt.error_word,
+                                rt.sms)
+                return True
             K.gemm_tc(a, self.weight, out, False, rt.workspace, rt.error_word, rt.sms, swiglu=True)
             return True
         if add_into is not None:

@@ -120,11 +120,12 @@ class RoutedExperts(Part):
         K.moe_route(z, E, top, E, ids, w, sg)
         if self.probe is not None:
             self.probe(self, step, ids)
-        # rows per tile of an expert's list: 64 where the tensor-core kernel runs (bfloat16), else
-        # 16 while an expert has few rows (a decode step), so that few multiply-adds are wasted
+        # rows per tile of an expert's list: 128 where the tensor-core kernel runs (bfloat16),
+        # else 64, or 16 while an expert has few rows (a decode step), so that few
+        # multiply-adds are wasted
         fast = self.rt.fast_kernels and self.w_up.dtype == torch.bfloat16 and self.hidden % 8 == 0 \
             and self.inter % 8 == 0
-        bm = 64 if fast or A > 16 * E else 16
+        bm = 128 if fast else (64 if A > 16 * E else 16)
         max_tiles = (A + bm - 1) // bm + E
         plan = torch.empty((2 + E + A + 2 * max_tiles,), dtype=torch.int32, device=dev)
         K.moe_plan(ids, E, bm, max_tiles, plan)

@@ -48,6 +48,7 @@ class DynamicTanh(Part):
     ``<name>.alpha`` and ``<name>.b``."""
     capturable = True
     accepts_pending = True
+    accepts_residual_bias = True   # forward(..., residual_bias=) adds it into x after norming
 
     def __init__(self, spec, prefix: str = ""):
         super().__init__(spec, prefix)
@@ -66,11 +67,11 @@ class DynamicTanh(Part):
         self.rt = rt
 
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None,
-                n_rows: Optional[int] = None, pending=None) -> torch.Tensor:
+                n_rows: Optional[int] = None, pending=None, residual_bias=None) -> torch.Tensor:
         R = n_rows if n_rows is not None else (rows.numel() if rows is not None else x.shape[0])
         out = torch.empty((R, self.size), dtype=self.rt.dtype, device=x.device)
         K.dynamic_tanh(x, self.weight, self.bias, self.alpha, out, rows, R,
-                       pending.partial if pending is not None else None)
+                       pending.partial if pending is not None else None, residual_bias)
         return out
 
 

@@ -289,10 +289,12 @@ def test_latent_attention_tensor_core_kernel(sizes):
     step = make_step([(slot, lens[slot] - 1, [0], []) for slot in range(3)])
     qd = rng.normal(size=(3, nh, kvr + rd))
     scratch = torch.empty((3 * nh * 16 * (kvr + 2),), dtype=torch.float32, device=DEV)
-    for splits in (1, 3, 16):
+    tickets = torch.zeros((8,), dtype=torch.int32, device=DEV)
+    for splits in (1, 3, 16, 3):
         out = torch.full((3, nh * kvr), 7.0, dtype=t, device=DEV)
         K.latent_attention_mma(dev(qd.reshape(3, -1), t), out, step, line, nh, kvr, rd, 0, 0.2,
-                               splits, scratch)
+                               splits, scratch, tickets)
+        assert int(tickets.abs().sum()) == 0         # the counters are left as they were found
         got = out.float().cpu().numpy().reshape(3, nh, kvr)
         for slot in range(3):
             want = plain_latent_attention(rounded(qd[slot], "bfloat16"),
@@ -354,7 +356,8 @@ def test_latent_attention_finds_one_far_key_and_no_later_one(dtype, past):
                 splits = int(kernel.split()[1])
                 scratch = torch.empty((nh * splits * (kvr + 2),), dtype=torch.float32, device=DEV)
                 K.latent_attention_mma(dev(q.reshape(1, -1), t), out, step, line, nh, kvr, rd, 0,
-                                       1.0, splits, scratch)
+                                       1.0, splits, scratch,
+                                       torch.zeros((4,), dtype=torch.int32, device=DEV))
             got = out.float().cpu().numpy().reshape(nh, kvr)
             assert np.abs(got - want).max() < 2e-2, (target, past, kernel)
 
