@@ -224,6 +224,10 @@ class BusavikConfig:
                               "gate": "gate", "up": "up", "down": "down"}})
             if mlp is not None:
                 norms["feed_forward"] = norm("norm2")
+            else:
+                # a layer without a feed-forward may still store its second norm: tolerated, unused
+                norms["spare"] = PartSpec("dynamic_tanh", {"name": "norm2", "size": c.width,
+                                                           "optional": True})
             layers.append(LayerSpec(block=PartSpec("prenorm_residual"), mixer=mixer,
                                     feed_forward=ff, norms=norms, prefix=f"l{i}."))
         schedule = tuple(Run(layer=l, cache_line=n, writes_cache=True)

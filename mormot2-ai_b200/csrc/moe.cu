@@ -285,14 +285,133 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* _
   });
 }
 
+// The two products for a decode step of at most eight tokens (tiles of at most 8 rows, so an
+// expert's weights are streamed exactly once): the WEIGHT rows are the 16 rows of the m16n8k16
+// product and the tile's tokens its 8 columns. A warp owns 16 output features (for the first
+// product their gate and their up rows) over all of K and reads its weight rows straight from
+// global memory into the product's registers, 16 bytes a thread and row, several steps of K in
+// flight; the tokens' rows wait in shared memory. Within a step of 32 values of K a thread
+// holds values 8t .. 8t+7 of both operands: the products pair them up in another order than
+// the instruction's own, which is the same sum. K must be a multiple of 32.
+#define MR_WARPS 4
+template <bool UP>
+__global__ void __launch_bounds__(MR_WARPS * 32)
+moe_rows_mma_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ W,
+                    void* __restrict__ out, const int* __restrict__ plan, int A, int E,
+                    int max_tiles, int top, int N, int K, int act,
+                    const float* __restrict__ weight) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  constexpr int NB = UP ? 2 : 1;
+  const int tile = blockIdx.y;
+  if (tile >= plan[0]) return;
+  const int* offsets = plan + 1;
+  const int* perm = offsets + E + 1;
+  const int e = perm[A + tile];
+  const int r0 = perm[A + max_tiles + tile];
+  const int rows = min(8, offsets[e + 1] - r0);
+  extern __shared__ __align__(16) unsigned char mr_raw[];
+  const int pitch = K + 8;
+  __nv_bfloat16* xs = (__nv_bfloat16*)mr_raw;  // [8][pitch]
+  __shared__ int src[8];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  if (tid < 8) src[tid] = tid < rows ? perm[r0 + tid] : -1;
+  __syncthreads();
+  for (int c = tid; c < 8 * (K / 8); c += MR_WARPS * 32) {
+    const int r = c / (K / 8), kc = (c - r * (K / 8)) * 8;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < rows) v = ldg16(in + (UP ? (size_t)(src[r] / top) : (size_t)(r0 + r)) * K + kc);
+    *(uint4*)(xs + r * pitch + kc) = v;
+  }
+  __syncthreads();
+  const int n0 = (blockIdx.x * MR_WARPS + warp) * 16;
+  if (n0 >= N) return;
+  const __nv_bfloat16* We = W + (size_t)e * NB * N * K;
+  // rows past N are read from row N - 1 and never stored
+  const __nv_bfloat16* wa[NB];
+  const __nv_bfloat16* wb[NB];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) {
+    wa[nb] = We + ((size_t)nb * N + min(n0 + g, N - 1)) * K + 8 * t;
+    wb[nb] = We + ((size_t)nb * N + min(n0 + g + 8, N - 1)) * K + 8 * t;
+  }
+  const __nv_bfloat16* xr = xs + g * pitch + 8 * t;
+  float acc[NB][4];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.f;
+  constexpr int UNROLL = UP ? 4 : 8;
+  for (int k0 = 0; k0 < K; k0 += 32 * UNROLL) {
+    uint4 a[UNROLL][NB], b[UNROLL][NB];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int k = k0 + 32 * u;
+      if (k < K) {
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          a[u][nb] = ldg16(wa[nb] + k);
+          b[u][nb] = ldg16(wb[nb] + k);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int k = k0 + 32 * u;
+      if (k < K) {
+        const uint4 x = *(const uint4*)(xr + k);
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          mma_bf16(acc[nb], a[u][nb].x, b[u][nb].x, a[u][nb].y, b[u][nb].y, x.x, x.y);
+          mma_bf16(acc[nb], a[u][nb].z, b[u][nb].z, a[u][nb].w, b[u][nb].w, x.z, x.w);
+        }
+      }
+    }
+  }
+  // acc[.][0..1]: feature n0 + g, tokens 2t and 2t + 1; acc[.][2..3]: feature n0 + g + 8
+#pragma unroll
+  for (int el = 0; el < 4; ++el) {
+    const int gn = n0 + g + (el >= 2 ? 8 : 0), r = 2 * t + (el & 1);
+    if (gn >= N || r >= rows) continue;
+    if (UP) {
+      ((__nv_bfloat16*)out)[(size_t)(r0 + r) * N + gn] =
+          __float2bfloat16_rn(moe_act(acc[0][el], act) * acc[NB - 1][el]);
+    } else {
+      const int a_ = src[r];
+      ((float*)out)[(size_t)a_ * N + gn] = weight[a_] * acc[0][el];
+    }
+  }
+}
+
 MB_EXPORT int mb_moe_gemm(const void* in, int dtype, const void* W, int w_dtype, void* out,
                           const int* plan, int A, int E, int max_tiles, int bm, int top, int N,
                           int K, int up, int act, const float* weight, void* stream) {
   if (A <= 0) return 0;
-  if (bm != 16 && bm != 64 && bm != 128) MB_FAIL("mb_moe_gemm: tiles of %d rows", bm);
+  if (bm != 8 && bm != 16 && bm != 64 && bm != 128) MB_FAIL("mb_moe_gemm: tiles of %d rows", bm);
   if (!up && weight == nullptr) MB_FAIL("mb_moe_gemm: the second product needs the weights");
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid((N + MG_BN - 1) / MG_BN, max_tiles);
+  if (bm == 8) {
+    if (!(dtype == MB_BF16 && w_dtype == MB_BF16 && K % 32 == 0 &&
+          (((uintptr_t)in | (uintptr_t)W) & 15) == 0))
+      MB_FAIL("mb_moe_gemm: tiles of 8 rows are the decode kernel's (bfloat16, K %% 32 == 0)");
+    const size_t smem = (size_t)8 * (K + 8) * 2;
+    if (smem > 160 * 1024) MB_FAIL("mb_moe_gemm: rows of %d values", K);
+    dim3 g8((N + 16 * MR_WARPS - 1) / (16 * MR_WARPS), max_tiles);
+#define GO8(UP_)                                                                              \
+  {                                                                                           \
+    static bool configured = false;                                                           \
+    if (!configured) {                                                                        \
+      cudaFuncSetAttribute(moe_rows_mma_kernel<UP_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                           160 * 1024);                                                       \
+      configured = true;                                                                      \
+    }                                                                                         \
+    mb_launch(moe_rows_mma_kernel<UP_>, g8, dim3(MR_WARPS * 32), smem, s,                     \
+              (const __nv_bfloat16*)in, (const __nv_bfloat16*)W, out, plan, A, E, max_tiles,  \
+              top, N, K, act, weight);                                                        \
+  }
+    if (up) GO8(true) else GO8(false)
+#undef GO8
+    MB_CHECK_LAUNCH("mb_moe_gemm");
+  }
   if (bm == 128) {
     if (!(dtype == MB_BF16 && w_dtype == MB_BF16 && K % 8 == 0 &&
           (((uintptr_t)in | (uintptr_t)W) & 15) == 0))

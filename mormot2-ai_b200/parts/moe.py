@@ -120,12 +120,14 @@ class RoutedExperts(Part):
         K.moe_route(z, E, top, E, ids, w, sg)
         if self.probe is not None:
             self.probe(self, step, ids)
-        # rows per tile of an expert's list: 128 where the tensor-core kernel runs (bfloat16),
-        # else 64, or 16 while an expert has few rows (a decode step), so that few
-        # multiply-adds are wasted
+        # rows per tile of an expert's list: 128 where the tensor-core kernel runs (bfloat16; 8
+        # for a decode step of at most 8 tokens, the form that reads weights into registers),
+        # else 64, or 16 while an expert has few rows, so that few multiply-adds are wasted
         fast = self.rt.fast_kernels and self.w_up.dtype == torch.bfloat16 and self.hidden % 8 == 0 \
             and self.inter % 8 == 0
         bm = 128 if fast else (64 if A > 16 * E else 16)
+        if fast and T <= 8 and self.hidden % 32 == 0 and self.inter % 32 == 0:
+            bm = 8      # a decode step: no expert has more rows, its weights stream once
         max_tiles = (A + bm - 1) // bm + E
         plan = torch.empty((2 + E + A + 2 * max_tiles,), dtype=torch.int32, device=dev)
         K.moe_plan(ids, E, bm, max_tiles, plan)

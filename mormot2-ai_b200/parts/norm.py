@@ -54,13 +54,18 @@ class DynamicTanh(Part):
         super().__init__(spec, prefix)
         self.size = int(spec.params["size"])
         self.name = prefix + spec.params["name"]
+        self.optional = bool(spec.params.get("optional", False))   # may be absent (and unused)
 
     def tensors(self) -> List[TensorNeed]:
-        return [TensorNeed(self.name, (self.size,), "vector"),
-                TensorNeed(self.name + ".b", (self.size,), "bias"),
-                TensorNeed(self.name + ".alpha", (), "vector")]
+        return [TensorNeed(self.name, (self.size,), "vector", optional=self.optional),
+                TensorNeed(self.name + ".b", (self.size,), "bias", optional=self.optional),
+                TensorNeed(self.name + ".alpha", (), "vector", optional=self.optional)]
 
     def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
+        self.rt = rt
+        if self.optional and self.name not in weights:
+            self.weight = self.bias = self.alpha = None
+            return
         self.weight, self.bias = weights[self.name], weights[self.name + ".b"]
         # the scalar stays on the device, as float32 whatever it was stored as
         self.alpha = weights[self.name + ".alpha"].to(torch.float32).reshape(1)

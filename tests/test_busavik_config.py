@@ -54,7 +54,9 @@ def test_tensor_names_and_shapes():
     for i, layer in enumerate(doc["layers"]):
         mlp = layer["mlp"]
         if mlp is None:
-            assert f"l{i}.norm2" not in needs and not any(k.startswith(f"l{i}.mlp") for k in needs)
+            assert not any(k.startswith(f"l{i}.mlp") for k in needs)
+            spare = [n for n in model.tensors() if n.name.startswith(f"l{i}.norm2")]
+            assert spare and all(n.optional for n in spare)    # tolerated when stored, never needed
         elif mlp["kind"] == "dense":
             assert needs[f"l{i}.mlp.gate.b"] == (mlp["ff"],)
             assert needs[f"l{i}.mlp.down.b"] == (w,)

@@ -395,17 +395,19 @@ def test_latent_attention_window_edges(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,E,top,shared,ff", [(3, 5, 1, 0, 14), (9, 6, 3, 20, 14),
-                                               (150, 4, 2, 12, 14), (150, 4, 2, 16, 40),
-                                               (5, 7, 3, 8, 16)])
-def test_routed_experts_part(dtype, T, E, top, shared, ff):
+@pytest.mark.parametrize("T,E,top,shared,ff,H", [
+    (3, 5, 1, 0, 14, 24), (9, 6, 3, 20, 14, 24), (150, 4, 2, 12, 14, 24),
+    (150, 4, 2, 16, 40, 24),        # bfloat16: 128-row tiles on the tensor cores
+    (5, 7, 3, 8, 16, 24),           # the same with few rows an expert
+    (5, 7, 3, 32, 32, 64),          # bfloat16: the decode form (at most 8 tokens, sizes % 32)
+    (8, 3, 2, 0, 96, 160)])         # the same with every expert chosen by several tokens
+def test_routed_experts_part(dtype, T, E, top, shared, ff, H):
     """The whole routed feed-forward (router, lists, both products, the sum) against the plain
     one; the router's rows are scaled so that no choice is a close call."""
     from mormot2_ai_b200.config.spec import PartSpec
     from mormot2_ai_b200.engine.runtime import Runtime
     from mormot2_ai_b200.parts import FEED_FORWARDS
     rng = np.random.default_rng(10 + T)
-    H = 24            # with ff a multiple of 8 the bfloat16 products run on the tensor cores
     t = TORCH[dtype]
     names = {"router": "router", "expert": "e{}.", "shared": "shared.",
              "shared_gate": "shared.sg", "gate": "gate", "up": "up", "down": "down"}
