@@ -374,11 +374,13 @@ def busavik_shapes(name):
     return BusavikConfig.from_dict(doc), twin
 
 
-def busavik_work(cfg, tokens, batch, held):
+def busavik_work(cfg, tokens, batch, held, experts_read=None):
     """Multiply-add work (FLOPs) of a prefill of one prompt of ``tokens`` tokens and bytes that a
     decode step of ``batch`` sequences holding ``held`` tokens together must read, by class of
     kernel, for either family. Attention of the latent form counts what its kernel does: every
-    head scores rows of kv_rank + rot_dim values and sums rows of kv_rank values."""
+    head scores rows of kv_rank + rot_dim values and sums rows of kv_rank values.
+    ``experts_read``: how many different experts a decode step's tokens chose (measured; with
+    random weights the tokens of a batch choose much the same ones), else the most possible."""
     pairs = tokens * (tokens + 1) / 2
     out = {"prefill_flops": {"attention": 0.0, "products": 0.0},
            "decode_bytes": {"attention": 0.0, "products": 0.0}}
@@ -396,7 +398,8 @@ def busavik_work(cfg, tokens, batch, held):
                 one = 3 * w * mlp["expert"]["ff"]
                 shared = 3 * w * mlp["shared"]["ff"] + w
                 ff_params = top * one + shared + e * w
-                ff_read = min(e, batch * top) * one + shared + e * w
+                chosen = min(e, batch * top) if experts_read is None else experts_read
+                ff_read = chosen * one + shared + e * w
             out["prefill_flops"]["products"] += 2 * tokens * (dense + per_head + ff_params)
             out["prefill_flops"]["attention"] += 2 * h * (kvr + rd + kvr) * pairs
             out["decode_bytes"]["products"] += 2 * (dense + per_head + ff_read)
@@ -432,7 +435,6 @@ def busavik_bench(a):
                                      max_context=max(ctx, tokens), max_slots=batch,
                                      prefill_chunk=4096, max_step_tokens=8192)
             sampler = DeviceSampler(eng.rt.device, eng.max_slots, eng.vocab_size)
-            work = busavik_work(cfg, tokens, batch, batch * (ctx - steps / 2.0))
             pms, pclocks = clocked(timed_prefill, torch, eng, [tokens])
             lens = [ctx - steps - warm - SETTLE] * batch
             (dms, held, launches), dclocks = clocked(timed_decode, torch, eng, sampler, Sampling(),
@@ -448,6 +450,12 @@ def busavik_bench(a):
             slots = [eng.open() for _ in range(batch)]
             eng.step([Entry(s, torch.randint(0, eng.vocab_size, (ctx - 8,), generator=gen).tolist())
                       for s in slots])
+            # how many different experts a decode step really reads
+            chosen = []
+            for layer in eng.model.layers:
+                if hasattr(layer.feed_forward, "probe"):
+                    layer.feed_forward.probe = lambda part, step, ids: chosen.append(
+                        int(ids.unique().numel()))
             dshares = {}
             for k in range(6):
                 _, sh, _ = eng.timed_step([Entry(s, [1 + k]) for s in slots])
@@ -455,11 +463,15 @@ def busavik_bench(a):
                     for name, ms in sh.items():
                         dshares[name] = dshares.get(name, 0.0) + ms / 4
             eng.rt.check()
+            experts_read = sum(chosen) / len(chosen) if chosen else None
+            work = busavik_work(cfg, tokens, batch, batch * (ctx - steps / 2.0), experts_read)
             flops, nbytes = work["prefill_flops"], work["decode_bytes"]
             points[f"{size}_{family}"] = {
                 "prefill_tokens_per_s": round(tokens / (pms / 1e3), 1), "prefill_ms": round(pms, 3),
                 "decode_tokens_per_s": round(batch * steps / (dms / 1e3), 1),
                 "decode_ms_per_step": round(dms / steps, 4), "decode_launches_per_step": launches // steps,
+                "experts_read_per_decode_step": experts_read,
+                "decode_gb_per_step": round(sum(nbytes.values()) / 1e9, 4),
                 "prefill_frac_bf16": round(sum(flops.values()) / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
                 "decode_frac_hbm": round(sum(nbytes.values()) / (dms / steps / 1e3) / (pk["hbm_gbs"] * 1e9), 4),
                 "prefill_kernels_ms": {k: round(v, 4) for k, v in sorted(pshares.items())},

@@ -270,6 +270,102 @@ heads_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, int lda_h,
   }
 }
 
+// The same product for a decode step of at most 16 tokens (bfloat16, K a multiple of 32): the
+// head's WEIGHT rows are the 16 rows of the m16n8k16 product and the tokens its columns (two
+// groups of eight). A warp owns 16 output features over all of K and reads its weight rows
+// straight from global memory into the product's registers, 16 bytes a thread and row, several
+// steps of K in flight; the tokens' rows of the head wait in shared memory. Within a step of 32
+// values of K a thread holds values 8t .. 8t+7 of both operands: the products pair them up in
+// another order than the instruction's own, which is the same sum.
+#define HR_WARPS 4
+__global__ void __launch_bounds__(HR_WARPS * 32)
+heads_rows_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda, int lda_h,
+                      const __nv_bfloat16* __restrict__ B, __nv_bfloat16* __restrict__ C, int ldc,
+                      int ldc_h, int M, int N, int K, const __nv_bfloat16* __restrict__ gate,
+                      int ldg, int tail, int rot_dims, const float* __restrict__ inv_freq,
+                      float amplitude, const int* __restrict__ tok_pos) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  extern __shared__ __align__(16) unsigned char hr_raw[];
+  const int pitch = K + 8;
+  __nv_bfloat16* xs = (__nv_bfloat16*)hr_raw;  // [16][pitch]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int h = blockIdx.y;
+  const __nv_bfloat16* Ah = A + (size_t)h * lda_h;
+  for (int c = tid; c < 16 * (K / 8); c += HR_WARPS * 32) {
+    const int r = c / (K / 8), kc = (c - r * (K / 8)) * 8;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < M) v = ldg16(Ah + (size_t)r * lda + kc);
+    *(uint4*)(xs + r * pitch + kc) = v;
+  }
+  __syncthreads();
+  if (tail > 0 && blockIdx.x == 0) {
+    const int half = rot_dims >> 1;
+    for (int e = tid; e < M * tail; e += HR_WARPS * 32) {
+      const int r = e / tail, i = e % tail;
+      const __nv_bfloat16* src = Ah + (size_t)r * lda + K;
+      float v = __bfloat162float(src[i]);
+      if (i < rot_dims) {
+        const int f = i < half ? i : i - half;
+        float sn, cs;
+        sincosf(inv_freq[f] * (float)tok_pos[r], &sn, &cs);
+        sn *= amplitude;
+        cs *= amplitude;
+        const float other = __bfloat162float(src[i < half ? i + half : i - half]);
+        v = i < half ? v * cs - other * sn : v * cs + other * sn;
+      }
+      C[(size_t)r * ldc + (size_t)h * ldc_h + N + i] = __float2bfloat16_rn(v);
+    }
+  }
+  const int n0 = (blockIdx.x * HR_WARPS + warp) * 16;
+  if (n0 >= N) return;
+  const __nv_bfloat16* Bh = B + (size_t)h * N * K;
+  const __nv_bfloat16* wa = Bh + (size_t)min(n0 + g, N - 1) * K + 8 * t;      // rows past N: read
+  const __nv_bfloat16* wb = Bh + (size_t)min(n0 + g + 8, N - 1) * K + 8 * t;  // again, not stored
+  const __nv_bfloat16* x0 = xs + g * pitch + 8 * t;
+  const __nv_bfloat16* x1 = x0 + 8 * pitch;
+  float acc[2][4];
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+  constexpr int UNROLL = 4;
+  for (int k0 = 0; k0 < K; k0 += 32 * UNROLL) {
+    uint4 a[UNROLL], b[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int k = k0 + 32 * u;
+      if (k < K) {
+        a[u] = ldg16(wa + k);
+        b[u] = ldg16(wb + k);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int k = k0 + 32 * u;
+      if (k < K) {
+        const uint4 xa = *(const uint4*)(x0 + k), xb = *(const uint4*)(x1 + k);
+        mma_bf16(acc[0], a[u].x, b[u].x, a[u].y, b[u].y, xa.x, xa.y);
+        mma_bf16(acc[0], a[u].z, b[u].z, a[u].w, b[u].w, xa.z, xa.w);
+        mma_bf16(acc[1], a[u].x, b[u].x, a[u].y, b[u].y, xb.x, xb.y);
+        mma_bf16(acc[1], a[u].z, b[u].z, a[u].w, b[u].w, xb.z, xb.w);
+      }
+    }
+  }
+  // acc[nt][0..1]: feature n0 + g, tokens 8 nt + 2t and + 1; acc[nt][2..3]: feature n0 + g + 8
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int el = 0; el < 4; ++el) {
+      const int gn = n0 + g + (el >= 2 ? 8 : 0), r = 8 * nt + 2 * t + (el & 1);
+      if (gn >= N || r >= M) continue;
+      float v = acc[nt][el];
+      if (gate) {
+        const float gv = __bfloat162float(gate[(size_t)r * ldg + (size_t)h * N + gn]);
+        v *= 1.0f / (1.0f + expf(-gv));
+      }
+      C[(size_t)r * ldc + (size_t)h * ldc_h + gn] = __float2bfloat16_rn(v);
+    }
+}
+
 MB_EXPORT int mb_heads_gemm(const void* A, int dtype, int lda, int lda_h, const void* B,
                             int b_dtype, void* C, int ldc, int ldc_h, int M, int N, int K,
                             int heads, const void* gate, int ldg, int tail, int rot_dims,
@@ -280,11 +376,26 @@ MB_EXPORT int mb_heads_gemm(const void* A, int dtype, int lda, int lda_h, const 
   if (tail > 0 && (rot_dims > tail || (rot_dims & 1) || (rot_dims > 0 && !inv_freq) || !tok_pos))
     MB_FAIL("mb_heads_gemm: %d rotating values of a tail of %d", rot_dims, tail);
   cudaStream_t s = (cudaStream_t)stream;
-  // bfloat16 operands whose rows start on 16-byte boundaries, and more than a few tokens: the
-  // tensor cores (a decode step's few rows stay with the kernel below, which streams each
-  // weight once with a sixteenth of the multiply-adds of a 64-row tile)
-  if (dtype == MB_BF16 && b_dtype == MB_BF16 && M > 16 && K % 8 == 0 && lda % 8 == 0 &&
-      lda_h % 8 == 0 && (((uintptr_t)A | (uintptr_t)B) & 15) == 0) {
+  // bfloat16 operands whose rows start on 16-byte boundaries go to the tensor cores: up to 16
+  // tokens (a decode step) to the form with the weight rows in the product's registers, more
+  // to 128 x 128 tiles
+  const bool aligned = dtype == MB_BF16 && b_dtype == MB_BF16 && K % 8 == 0 && lda % 8 == 0 &&
+                       lda_h % 8 == 0 && (((uintptr_t)A | (uintptr_t)B) & 15) == 0;
+  if (aligned && M <= 16 && K % 32 == 0 && (size_t)16 * (K + 8) * 2 <= 96 * 1024) {
+    const size_t smem = (size_t)16 * (K + 8) * 2;
+    static bool configured = false;
+    if (!configured) {
+      cudaFuncSetAttribute(heads_rows_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           96 * 1024);
+      configured = true;
+    }
+    mb_launch(heads_rows_mma_kernel, dim3((N + 16 * HR_WARPS - 1) / (16 * HR_WARPS), heads),
+              dim3(HR_WARPS * 32), smem, s, (const __nv_bfloat16*)A, lda, lda_h,
+              (const __nv_bfloat16*)B, (__nv_bfloat16*)C, ldc, ldc_h, M, N, K,
+              (const __nv_bfloat16*)gate, ldg, tail, rot_dims, inv_freq, amplitude, tok_pos);
+    MB_CHECK_LAUNCH("mb_heads_gemm");
+  }
+  if (aligned && M > 16) {
     mb_launch(heads_gemm_mma_kernel, dim3((N + 127) / 128, (M + MT_BM - 1) / MT_BM, heads),
               dim3(MT_THREADS), 0, s, (const __nv_bfloat16*)A, lda, lda_h, (const __nv_bfloat16*)B,
               (__nv_bfloat16*)C, ldc, ldc_h, M, N, K, (const __nv_bfloat16*)gate, ldg, tail,

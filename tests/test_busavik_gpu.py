@@ -198,9 +198,12 @@ def test_latent_prep_kernel_writes_normed_latents_and_the_rotated_part(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("M,Kd,tail", [(3, 10, 6), (70, 10, 6), (150, 40, 8)])
+@pytest.mark.parametrize("M,Kd,tail", [(3, 10, 6), (70, 10, 6), (150, 40, 8), (3, 64, 8),
+                                       (13, 96, 16)])
 def test_heads_gemm_kernel(dtype, M, Kd, tail):
-    """The last case has rows on 16-byte boundaries and goes to the tensor cores in bfloat16."""
+    """The last three cases have rows on 16-byte boundaries and go to the tensor cores in
+    bfloat16: 128-row tiles, and for at most 16 tokens the form that reads weights into
+    registers."""
     rng = np.random.default_rng(4)
     H, N, dims = 3, 21, 4
     t = TORCH[dtype]
