@@ -43,6 +43,9 @@ __device__ __forceinline__ float rotated(const float* buf, int i, int rot_dims,
 // (kv_rank values at column kv_col) and behind it the shared key part (rot_dim values).
 // cq_out [T, q_rank] = w_q · rmsnorm(query latent); the cache row of the token's slot and
 // position = [w_kv · rmsnorm(key/value latent) ; rotate(shared key part)].
+// With parts > 0 the rows are read from `partial` [parts][T, ld] (float32, the split sums of
+// the product that made them, added up here in split order) instead of f, and gate_n further
+// columns from gate_col on are added up too and written to gate_out [T, gate_n].
 template <typename T, typename TW>
 __global__ void __launch_bounds__(128)
 latent_prep_kernel(const T* __restrict__ f, int ld, int q_col, int kv_col, int q_rank, int kv_rank,
@@ -50,27 +53,39 @@ latent_prep_kernel(const T* __restrict__ f, int ld, int q_col, int kv_col, int q
                    const float* __restrict__ inv_freq, int rot_dims, float amplitude,
                    const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
                    const int* __restrict__ page_table, int max_pages, int ring_pages,
-                   T* __restrict__ pool, T* __restrict__ cq_out, int write_cache) {
+                   T* __restrict__ pool, T* __restrict__ cq_out, int write_cache,
+                   const float* __restrict__ partial, int parts, size_t part_stride,
+                   T* __restrict__ gate_out, int gate_col, int gate_n) {
   mb_grid_wait();
   mb_grid_launch_next();
   extern __shared__ float buf[];  // q_rank + kv_rank + rot_dim
   __shared__ float red[33];
   const int t = blockIdx.x;
   const T* row = f + (size_t)t * ld;
+  const float* prow = partial + (size_t)t * ld;
+  auto value = [&](int col) -> float {
+    if (parts == 0) return to_f32<T>(row[col]);
+    float v = prow[col];
+    for (int p = 1; p < parts; ++p) v += prow[p * part_stride + col];
+    return v;
+  };
   float* bq = buf;
   float* bc = buf + q_rank;
   float* br = bc + kv_rank;
   float sq = 0.f, sc = 0.f;
   for (int i = threadIdx.x; i < q_rank; i += blockDim.x) {
-    const float v = to_f32<T>(row[q_col + i]);
+    const float v = value(q_col + i);
     bq[i] = v;
     sq = fmaf(v, v, sq);
   }
   for (int i = threadIdx.x; i < kv_rank + rot_dim; i += blockDim.x) {
-    const float v = to_f32<T>(row[kv_col + i]);
+    const float v = value(kv_col + i);
     bc[i] = v;
     if (i < kv_rank) sc = fmaf(v, v, sc);
   }
+  if (parts > 0 && gate_out)
+    for (int i = threadIdx.x; i < gate_n; i += blockDim.x)
+      gate_out[(size_t)t * gate_n + i] = from_f32<T>(value(gate_col + i));
   sq = block_sum(sq, red);
   sc = block_sum(sc, red);
   if (q_rank > 0) {
@@ -95,8 +110,12 @@ MB_EXPORT int mb_latent_prep(const void* f, int dtype, int ld, int q_col, int kv
                              int w_dtype, float eps, const float* inv_freq, int rot_dims,
                              float amplitude, const int* tok_slot, const int* tok_pos,
                              const int* page_table, int max_pages, int ring_pages, void* pool,
-                             void* cq_out, int T, int write_cache, void* stream) {
+                             void* cq_out, int T, int write_cache, const float* partial,
+                             int parts, long long part_stride, void* gate_out, int gate_col,
+                             int gate_n, void* stream) {
   if (T <= 0) return 0;
+  if ((parts > 0) != (partial != nullptr) || (parts == 0 && f == nullptr))
+    MB_FAIL("mb_latent_prep: rows or their split sums");
   if (rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1))
     MB_FAIL("mb_latent_prep: %d rotating values of %d", rot_dims, rot_dim);
   if (rot_dims > 0 && inv_freq == nullptr) MB_FAIL("mb_latent_prep: no frequencies");
@@ -107,7 +126,8 @@ MB_EXPORT int mb_latent_prep(const void* f, int dtype, int ld, int q_col, int kv
   mb_launch(latent_prep_kernel<T_, TW_>, dim3(T), dim3(128), smem, s, (const T_*)f, ld, q_col, \
             kv_col, q_rank, kv_rank, rot_dim, (const TW_*)w_q, (const TW_*)w_kv, eps, inv_freq, \
             rot_dims, amplitude, tok_slot, tok_pos, page_table, max_pages, ring_pages,       \
-            (T_*)pool, (T_*)cq_out, write_cache)
+            (T_*)pool, (T_*)cq_out, write_cache, partial, parts, (size_t)part_stride,        \
+            (T_*)gate_out, gate_col, gate_n)
   if (dtype == MB_F32) {
     if (w_dtype == MB_F32) GO(float, float); else GO(float, __nv_bfloat16);
   } else {

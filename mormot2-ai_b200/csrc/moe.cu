@@ -21,17 +21,20 @@
 MB_DEFINE_LAST_ERROR
 
 // ------------------------------------------------------------------ route
-// z [T, ldz] float32: columns [0, E) the experts' logits, column shared_col (or -1) the shared
-// expert's gate logit. One warp per token.
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ z, int ldz, int E, int top, int shared_col,
-                 int* __restrict__ ids, float* __restrict__ w, float* __restrict__ sg, int T) {
-  mb_grid_wait();
-  mb_grid_launch_next();
-  const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (t >= T) return;
-  const float* zr = z + (size_t)t * ldz;
+// z [parts][T, ldz] float32, the split sums of the router's product (parts = 1: the product
+// itself), added up as they are read: columns [0, E) the experts' logits, column shared_col
+// (or -1) the shared expert's gate logit. One warp per token.
+__device__ __forceinline__ float route_logit(const float* __restrict__ zr, int parts,
+                                             size_t part_stride, int i) {
+  float v = zr[i];
+  for (int p = 1; p < parts; ++p) v += zr[p * part_stride + i];
+  return v;
+}
+
+__device__ __forceinline__ void route_token(const float* __restrict__ zr, int parts,
+                                            size_t part_stride, int E, int top, int shared_col,
+                                            int* __restrict__ ids, float* __restrict__ w,
+                                            float* __restrict__ sg, int lane) {
   float last_v = INFINITY;
   int last_i = -1;
   float first = 0.f, sum = 0.f, mine = 0.f;  // lane k keeps the k-th chosen logit
@@ -39,7 +42,7 @@ moe_route_kernel(const float* __restrict__ z, int ldz, int E, int top, int share
     float best = -INFINITY;
     int best_i = 0x7fffffff;
     for (int i = lane; i < E; i += 32) {
-      const float v = zr[i];
+      const float v = route_logit(zr, parts, part_stride, i);
       const bool open = v < last_v || (v == last_v && i > last_i);
       if (open && (v > best || (v == best && i < best_i))) {
         best = v;
@@ -57,27 +60,42 @@ moe_route_kernel(const float* __restrict__ z, int ldz, int E, int top, int share
     }
     if (best_i == 0x7fffffff) {  // nothing left that compares (NaNs): take the next index
       best_i = min(E - 1, last_i + 1);
-      best = zr[best_i];
+      best = route_logit(zr, parts, part_stride, best_i);
     }
     if (k == 0) first = best;
     const float e = expf(best - first);
     sum += e;
     if (lane == k) mine = e;
-    if (lane == 0) ids[(size_t)t * top + k] = best_i;
+    if (lane == 0) ids[k] = best_i;
     last_v = best;
     last_i = best_i;
   }
-  if (lane < top) w[(size_t)t * top + lane] = mine / sum;
-  if (sg && lane == 0) sg[t] = 1.0f / (1.0f + expf(-zr[shared_col]));
+  if (lane < top) w[lane] = mine / sum;
+  if (sg && lane == 0) *sg = 1.0f / (1.0f + expf(-route_logit(zr, parts, part_stride, shared_col)));
 }
 
-MB_EXPORT int mb_moe_route(const float* z, int ldz, int E, int top, int shared_col, int* ids,
-                           float* w, float* sg, int T, void* stream) {
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ z, int ldz, int parts, size_t part_stride, int E,
+                 int top, int shared_col, int* __restrict__ ids, float* __restrict__ w,
+                 float* __restrict__ sg, int T) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  route_token(z + (size_t)t * ldz, parts, part_stride, E, top, shared_col, ids + (size_t)t * top,
+              w + (size_t)t * top, sg ? sg + t : nullptr, lane);
+}
+
+MB_EXPORT int mb_moe_route(const float* z, int ldz, int parts, long long part_stride, int E,
+                           int top, int shared_col, int* ids, float* w, float* sg, int T,
+                           void* stream) {
   if (T <= 0) return 0;
   if (top <= 0 || top > 32 || top > E) MB_FAIL("mb_moe_route: %d of %d experts", top, E);
   if ((sg != nullptr) != (shared_col >= 0)) MB_FAIL("mb_moe_route: the shared gate and its column");
-  mb_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, (cudaStream_t)stream, z, ldz, E,
-            top, shared_col, ids, w, sg, T);
+  if (parts < 1) MB_FAIL("mb_moe_route: %d parts", parts);
+  mb_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, (cudaStream_t)stream, z, ldz,
+            parts, (size_t)part_stride, E, top, shared_col, ids, w, sg, T);
   MB_CHECK_LAUNCH("mb_moe_route");
 }
 
@@ -85,12 +103,23 @@ MB_EXPORT int mb_moe_route(const float* z, int ldz, int E, int top, int shared_c
 // plan (int32): [0] number of tiles, [1 .. 1+E] first list row of every expert (E + 1 values),
 // then perm[A] (the assignment a = t·top + k at every list row), then tile_expert[max_tiles]
 // and tile_row0[max_tiles]. One block.
+// With z given (a step of at most 64 tokens) the block first routes the tokens itself, a warp a
+// token, and writes ids, w and sg as moe_route does: one kernel instead of two.
 __global__ void __launch_bounds__(1024)
-moe_plan_kernel(const int* __restrict__ ids, int A, int E, int bm, int max_tiles,
-                int* __restrict__ plan) {
+moe_plan_kernel(int* __restrict__ ids, int A, int E, int bm, int max_tiles,
+                int* __restrict__ plan, const float* __restrict__ z, int ldz, int parts,
+                size_t part_stride, int top, int shared_col, float* __restrict__ w,
+                float* __restrict__ sg) {
   mb_grid_wait();
   mb_grid_launch_next();
   extern __shared__ int counts[];  // E counters, then E cursors
+  if (z != nullptr) {
+    const int T = A / top, lane = threadIdx.x & 31;
+    for (int t = threadIdx.x >> 5; t < T; t += blockDim.x >> 5)
+      route_token(z + (size_t)t * ldz, parts, part_stride, E, top, shared_col,
+                  ids + (size_t)t * top, w + (size_t)t * top, sg ? sg + t : nullptr, lane);
+    __syncthreads();  // the block's own writes of ids are visible to it
+  }
   int* cursor = counts + E;
   int* offsets = plan + 1;
   int* perm = offsets + E + 1;
@@ -125,14 +154,32 @@ moe_plan_kernel(const int* __restrict__ ids, int A, int E, int bm, int max_tiles
   }
 }
 
-MB_EXPORT int mb_moe_plan(const int* ids, int A, int E, int bm, int max_tiles, int* plan,
+MB_EXPORT int mb_moe_plan(int* ids, int A, int E, int bm, int max_tiles, int* plan,
                           void* stream) {
   if (A <= 0) return 0;
   if (E > 4096) MB_FAIL("mb_moe_plan: %d experts", E);
   if (max_tiles < (A + bm - 1) / bm + E) MB_FAIL("mb_moe_plan: room for %d tiles", max_tiles);
   mb_launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int),
-            (cudaStream_t)stream, ids, A, E, bm, max_tiles, plan);
+            (cudaStream_t)stream, ids, A, E, bm, max_tiles, plan, (const float*)nullptr, 0, 1,
+            (size_t)0, 1, -1, (float*)nullptr, (float*)nullptr);
   MB_CHECK_LAUNCH("mb_moe_plan");
+}
+
+// moe_route and moe_plan in one kernel, for a step of at most 64 tokens.
+MB_EXPORT int mb_moe_route_plan(const float* z, int ldz, int parts, long long part_stride, int E,
+                                int top, int shared_col, int* ids, float* w, float* sg, int T,
+                                int bm, int max_tiles, int* plan, void* stream) {
+  if (T <= 0) return 0;
+  if (T > 64) MB_FAIL("mb_moe_route_plan: %d tokens (at most 64)", T);
+  if (top <= 0 || top > 32 || top > E) MB_FAIL("mb_moe_route_plan: %d of %d experts", top, E);
+  if ((sg != nullptr) != (shared_col >= 0)) MB_FAIL("mb_moe_route_plan: the shared gate and its column");
+  if (E > 4096 || parts < 1) MB_FAIL("mb_moe_route_plan: %d experts, %d parts", E, parts);
+  const int A = T * top;
+  if (max_tiles < (A + bm - 1) / bm + E) MB_FAIL("mb_moe_route_plan: room for %d tiles", max_tiles);
+  mb_launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int),
+            (cudaStream_t)stream, ids, A, E, bm, max_tiles, plan, z, ldz, parts,
+            (size_t)part_stride, top, shared_col, w, sg);
+  MB_CHECK_LAUNCH("mb_moe_route_plan");
 }
 
 // ------------------------------------------------------------------ the experts' products
@@ -445,10 +492,11 @@ MB_EXPORT int mb_moe_gemm(const void* in, int dtype, const void* W, int w_dtype,
 }
 
 // ------------------------------------------------------------------ combine
-// x[t, c] += sum_k y[(t·top + k), c] (k ascending) + sg[t] · shared[t, c]
+// x[t, c] += sum_k y[(t·top + k), c] (k ascending) + sg[t] · shared[t, c]; shared
+// [parts][T, H]: the split sums of the shared expert's last product, added up in split order.
 __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ y, int top,
-                                   const float* __restrict__ shared, const float* __restrict__ sg,
-                                   int H) {
+                                   const float* __restrict__ shared, int parts,
+                                   size_t part_stride, const float* __restrict__ sg, int H) {
   mb_grid_wait();
   mb_grid_launch_next();
   const int t = blockIdx.x;
@@ -456,15 +504,19 @@ __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restric
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     float v = 0.f;
     for (int k = 0; k < top; ++k) v += y[((size_t)t * top + k) * H + c];
-    if (shared) v = fmaf(g, shared[(size_t)t * H + c], v);
+    if (shared) {
+      float sh = shared[(size_t)t * H + c];
+      for (int p = 1; p < parts; ++p) sh += shared[p * part_stride + (size_t)t * H + c];
+      v = fmaf(g, sh, v);
+    }
     x[(size_t)t * H + c] += v;
   }
 }
 
-MB_EXPORT int mb_moe_combine(float* x, const float* y, int top, const float* shared,
-                             const float* sg, int T, int H, void* stream) {
+MB_EXPORT int mb_moe_combine(float* x, const float* y, int top, const float* shared, int parts,
+                             long long part_stride, const float* sg, int T, int H, void* stream) {
   if (T <= 0) return 0;
   mb_launch(moe_combine_kernel, dim3(T), dim3(H >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, x,
-            y, top, shared, sg, H);
+            y, top, shared, parts, (size_t)part_stride, sg, H);
   MB_CHECK_LAUNCH("mb_moe_combine");
 }

@@ -72,7 +72,7 @@ CLASS_OF = {"mb_gemm_tc": "products", "mb_gemm_simt": "products",
             "mb_gemm_tc_gated": "products", "mb_latent_prep": "rotary",
             "mb_heads_gemm": "products", "mb_latent_attention": "attention",
             "mb_latent_attention_mma": "attention",
-            "mb_moe_route": "routing", "mb_moe_plan": "routing", "mb_moe_gemm": "products",
+            "mb_moe_route": "routing", "mb_moe_plan": "routing", "mb_moe_route_plan": "routing", "mb_moe_gemm": "products",
             "mb_moe_combine": "routing"}
 
 
@@ -314,24 +314,40 @@ def scale_rows(x: torch.Tensor, factor: float) -> None:
 
 
 # ------------------------------------------------------------------------------ latent attention
-def latent_prep(f: torch.Tensor, q_col: int, kv_col: int, q_rank: int, kv_rank: int, rot_dim: int,
-                w_q: torch.Tensor, w_kv: torch.Tensor, eps: float,
+def latent_prep(f: Optional[torch.Tensor], q_col: int, kv_col: int, q_rank: int, kv_rank: int,
+                rot_dim: int, w_q: torch.Tensor, w_kv: torch.Tensor, eps: float,
                 inv_freq: Optional[torch.Tensor], rot_dims: int, amplitude: float, step, line,
-                cq_out: torch.Tensor, write_cache: bool) -> None:
+                cq_out: torch.Tensor, write_cache: bool, partial: Optional[torch.Tensor] = None,
+                gate_out: Optional[torch.Tensor] = None, gate_col: int = 0) -> None:
     """From the rows of ``f`` [T, ld]: the normed query latent into ``cq_out`` [T, q_rank] and
-    the cache row [normed key/value latent ; rotated shared key part] of every token."""
-    T = f.shape[0]
-    assert f.stride(1) == 1 and cq_out.is_contiguous() and cq_out.dtype == f.dtype
-    assert w_q.dtype == w_kv.dtype and line.k.dtype == f.dtype
+    the cache row [normed key/value latent ; rotated shared key part] of every token.
+    ``partial`` [parts, T, ld] float32 stands for ``f`` (then None): the split sums of the
+    product, added up here; the columns from ``gate_col`` on are then added up into
+    ``gate_out`` [T, n] as well."""
+    T = cq_out.shape[0]
+    assert cq_out.is_contiguous() and cq_out.dtype == line.k.dtype
+    assert w_q.dtype == w_kv.dtype
     assert line.head_dim == kv_rank + rot_dim and line.kv_heads == 1
+    parts, stride, gate_n = 0, 0, 0
+    if partial is not None:
+        assert f is None and partial.dtype == torch.float32 and partial.is_contiguous()
+        parts, stride, ld = partial.shape[0], partial.stride(0), partial.shape[2]
+        if gate_out is not None:
+            assert gate_out.is_contiguous() and gate_out.dtype == cq_out.dtype
+            gate_n = gate_out.shape[1]
+            assert gate_col + gate_n <= ld
+    else:
+        assert f.stride(1) == 1 and f.dtype == cq_out.dtype and gate_out is None
+        ld = f.stride(0)
     _call("latent", "mb_latent_prep",
           [_vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _vp, _i, _f, _vp, _vp, _vp, _i, _i,
-           _vp, _vp, _i, _i, _vp],
-          _ptr(f), code_of(f.dtype), f.stride(0), q_col, kv_col, q_rank, kv_rank, rot_dim,
+           _vp, _vp, _i, _i, _vp, _i, _ll, _vp, _i, _i, _vp],
+          _ptr(f), code_of(cq_out.dtype), ld, q_col, kv_col, q_rank, kv_rank, rot_dim,
           _ptr(w_q), _ptr(w_kv), code_of(w_q.dtype), float(eps), _ptr(inv_freq), rot_dims,
           float(amplitude), _ptr(step.tok_slot), _ptr(step.tok_pos), _ptr(line.page_table),
           line.max_pages, line.ring_pages, _ptr(line.k), _ptr(cq_out), T,
-          1 if write_cache else 0, _stream())
+          1 if write_cache else 0, _ptr(partial), parts, stride, _ptr(gate_out), gate_col,
+          gate_n, _stream())
 
 
 def heads_gemm(a: torch.Tensor, lda_h: int, b: torch.Tensor, c: torch.Tensor, ldc_h: int,
@@ -396,17 +412,25 @@ def latent_attention_mma(q: torch.Tensor, out: torch.Tensor, step, line, nh: int
 
 
 # ------------------------------------------------------------------------------ routed experts
+def _parts_of(z: torch.Tensor):
+    """z [T, N] or [parts, T, N] float32 (the split sums of a product): pointer arguments."""
+    assert z.dtype == torch.float32 and z.stride(-1) == 1
+    if z.dim() == 2:
+        return 1, 0, z.stride(0)
+    assert z.dim() == 3
+    return z.shape[0], z.stride(0), z.stride(1)
+
+
 def moe_route(z: torch.Tensor, experts: int, top: int, shared_col: int, ids: torch.Tensor,
               w: torch.Tensor, sg: Optional[torch.Tensor]) -> None:
-    """Per row of z (float32 router logits): the ``top`` largest of the first ``experts``
-    columns into ``ids`` and the softmax over them into ``w``; ``sg`` = sigmoid of column
-    ``shared_col``."""
-    T = z.shape[0]
-    assert z.dtype == torch.float32 and z.stride(1) == 1
+    """Per row of z (float32 router logits, [T, N] or the split sums [parts, T, N] of the
+    router's product): the ``top`` largest of the first ``experts`` columns into ``ids`` and
+    the softmax over them into ``w``; ``sg`` = sigmoid of column ``shared_col``."""
+    parts, stride, ldz = _parts_of(z)
     assert ids.dtype == torch.int32 and w.dtype == torch.float32
-    _call("moe", "mb_moe_route", [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
-          _ptr(z), z.stride(0), experts, top, shared_col if sg is not None else -1, _ptr(ids),
-          _ptr(w), _ptr(sg), T, _stream())
+    _call("moe", "mb_moe_route", [_vp, _i, _i, _ll, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
+          _ptr(z), ldz, parts, stride, experts, top, shared_col if sg is not None else -1,
+          _ptr(ids), _ptr(w), _ptr(sg), z.shape[-2], _stream())
 
 
 def moe_plan(ids: torch.Tensor, experts: int, bm: int, max_tiles: int,
@@ -414,6 +438,19 @@ def moe_plan(ids: torch.Tensor, experts: int, bm: int, max_tiles: int,
     assert plan.dtype == torch.int32 and plan.numel() >= 2 + experts + ids.numel() + 2 * max_tiles
     _call("moe", "mb_moe_plan", [_vp, _i, _i, _i, _i, _vp, _vp],
           _ptr(ids), ids.numel(), experts, bm, max_tiles, _ptr(plan), _stream())
+
+
+def moe_route_plan(z: torch.Tensor, experts: int, top: int, shared_col: int, ids: torch.Tensor,
+                   w: torch.Tensor, sg: Optional[torch.Tensor], bm: int, max_tiles: int,
+                   plan: torch.Tensor) -> None:
+    """``moe_route`` and ``moe_plan`` as one kernel, for a step of at most 64 tokens."""
+    parts, stride, ldz = _parts_of(z)
+    assert ids.dtype == torch.int32 and w.dtype == torch.float32
+    assert plan.dtype == torch.int32 and plan.numel() >= 2 + experts + ids.numel() + 2 * max_tiles
+    _call("moe", "mb_moe_route_plan",
+          [_vp, _i, _i, _ll, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp],
+          _ptr(z), ldz, parts, stride, experts, top, shared_col if sg is not None else -1,
+          _ptr(ids), _ptr(w), _ptr(sg), z.shape[-2], bm, max_tiles, _ptr(plan), _stream())
 
 
 def moe_gemm(src: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: torch.Tensor,
@@ -437,14 +474,17 @@ def moe_gemm(src: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: torch.
 
 def moe_combine(x: torch.Tensor, y: torch.Tensor, top: int, shared: Optional[torch.Tensor],
                 sg: Optional[torch.Tensor]) -> None:
-    """x[t] += sum_k y[t*top + k] + sg[t] * shared[t] (all float32)."""
+    """x[t] += sum_k y[t*top + k] + sg[t] * shared[t] (all float32); ``shared`` [T, H] or the
+    split sums [parts, T, H] of the shared expert's last product."""
     T, H = x.shape
     assert x.dtype == y.dtype == torch.float32 and y.shape == (T * top, H)
     _contig(x, "x"), _contig(y, "y")
+    parts, stride = 1, 0
     if shared is not None:
-        assert shared.dtype == torch.float32 and shared.shape == (T, H) and shared.is_contiguous()
-    _call("moe", "mb_moe_combine", [_vp, _vp, _i, _vp, _vp, _i, _i, _vp],
-          _ptr(x), _ptr(y), top, _ptr(shared), _ptr(sg), T, H, _stream())
+        assert shared.shape[-2:] == (T, H) and shared.is_contiguous()
+        parts, stride, _ = _parts_of(shared)
+    _call("moe", "mb_moe_combine", [_vp, _vp, _i, _vp, _i, _ll, _vp, _i, _i, _vp],
+          _ptr(x), _ptr(y), top, _ptr(shared), parts, stride, _ptr(sg), T, H, _stream())
 
 
 # ------------------------------------------------------------------------------ products

@@ -97,10 +97,19 @@ class LatentAttention(Part):
         amplitude = float(getattr(self.position, "amplitude", 1.0))
         if rot_dims > rd:
             raise ConfigError(f"{rot_dims} rotating values of a part of {rd}")
-        f = self.down(h)                                               # [T, qr + kvr + rd (+ nh vd)]
+        # [T, qr + kvr + rd (+ nh vd)], or (few tokens) the product's split sums, which the kernel
+        # that norms the latents adds up as it reads them
+        f = self.down(h, defer=True)
         cq = torch.empty((T, qr), dtype=dt, device=dev)
-        K.latent_prep(f, 0, self.kv_col, qr, kvr, rd, self.q_norm, self.kv_norm, self.eps,
-                      inv_freq, rot_dims, amplitude, step, line, cq, writes_cache)
+        if isinstance(f, Pending):
+            gate = torch.empty((T, nh * vd), dtype=dt, device=dev) if self.gated else None
+            K.latent_prep(None, 0, self.kv_col, qr, kvr, rd, self.q_norm, self.kv_norm, self.eps,
+                          inv_freq, rot_dims, amplitude, step, line, cq, writes_cache,
+                          partial=f.partial, gate_out=gate, gate_col=self.gate_col)
+        else:
+            gate = f[:, self.gate_col:] if self.gated else None
+            K.latent_prep(f, 0, self.kv_col, qr, kvr, rd, self.q_norm, self.kv_norm, self.eps,
+                          inv_freq, rot_dims, amplitude, step, line, cq, writes_cache)
         q = self.uq(cq)                                                # [T, nh (dim + rd)]
         ql = torch.empty((T, nh * (kvr + rd)), dtype=dt, device=dev)
         K.heads_gemm(q, dim + rd, self.uk_t, ql, kvr + rd, tail=rd, rot_dims=rot_dims,
@@ -108,8 +117,7 @@ class LatentAttention(Part):
         ol = torch.empty((T, nh * kvr), dtype=dt, device=dev)
         self.rt.latent_attention(ql, ol, step, line, nh, kvr, rd, self.window, self.scale)
         heads = torch.empty((T, nh * vd), dtype=dt, device=dev)
-        K.heads_gemm(ol, kvr, self.uv, heads, vd,
-                     gate=f[:, self.gate_col:] if self.gated else None)
+        K.heads_gemm(ol, kvr, self.uv, heads, vd, gate=gate)
         out = self.o(heads, add_into=x, defer=True)
         return out if isinstance(out, Pending) else None
 

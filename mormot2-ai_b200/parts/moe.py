@@ -21,7 +21,12 @@ import torch
 from .. import kernels as K
 from ..errors import ConfigError
 from .base import FEED_FORWARDS, Part, TensorNeed
-from .linear import Linear
+from .linear import Linear, Pending
+
+
+def _sums(result):
+    """A product's float32 result [T, N], or its pending split sums as [parts, T, N]."""
+    return result.partial if isinstance(result, Pending) else result
 
 
 class RoutedExperts(Part):
@@ -113,13 +118,11 @@ class RoutedExperts(Part):
         T, dev = h.shape[0], h.device
         E, top = self.experts, self.top
         A = T * top
-        z = self.router(h, out_dtype=torch.float32)                      # [T, E (+ 1)]
+        # [T, E (+ 1)] float32, or the split sums of the product, which the router adds up
+        z = _sums(self.router(h, out_dtype=torch.float32, defer=True))
         ids = torch.empty((T, top), dtype=torch.int32, device=dev)
         w = torch.empty((T, top), dtype=torch.float32, device=dev)
         sg = torch.empty((T,), dtype=torch.float32, device=dev) if self.shared_size else None
-        K.moe_route(z, E, top, E, ids, w, sg)
-        if self.probe is not None:
-            self.probe(self, step, ids)
         # rows per tile of an expert's list: 128 where the tensor-core kernel runs (bfloat16; 8
         # for a decode step of at most 8 tokens, the form that reads weights into registers),
         # else 64, or 16 while an expert has few rows, so that few multiply-adds are wasted
@@ -130,7 +133,13 @@ class RoutedExperts(Part):
             bm = 8      # a decode step: no expert has more rows, its weights stream once
         max_tiles = (A + bm - 1) // bm + E
         plan = torch.empty((2 + E + A + 2 * max_tiles,), dtype=torch.int32, device=dev)
-        K.moe_plan(ids, E, bm, max_tiles, plan)
+        if T <= 64:          # the router's choice and the lists in one kernel
+            K.moe_route_plan(z, E, top, E, ids, w, sg, bm, max_tiles, plan)
+        else:
+            K.moe_route(z, E, top, E, ids, w, sg)
+            K.moe_plan(ids, E, bm, max_tiles, plan)
+        if self.probe is not None:
+            self.probe(self, step, ids)
         act = torch.empty((A, self.inter), dtype=self.rt.dtype, device=dev)
         K.moe_gemm(h, self.w_up, act, plan, A, max_tiles, bm, top, True, self.act)
         y = torch.empty((A, self.hidden), dtype=torch.float32, device=dev)
@@ -143,7 +152,7 @@ class RoutedExperts(Part):
                 gu = self.shared_up(h)
                 sa = torch.empty((T, self.shared_size), dtype=self.rt.dtype, device=dev)
                 K.gated_act(gu, sa, self.act)
-            shared = self.shared_down(sa, out_dtype=torch.float32)
+            shared = _sums(self.shared_down(sa, out_dtype=torch.float32, defer=True))
         K.moe_combine(x, y, top, shared, sg)
         return None
 

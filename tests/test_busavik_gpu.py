@@ -195,6 +195,20 @@ def test_latent_prep_kernel_writes_normed_latents_and_the_rotated_part(dtype):
         assert np.abs(got - want).max() < tol * np.abs(want).max(), i
     # the values behind the rotating ones pass as they are
     assert np.allclose(want_r[:, dims:], fr[:, 5 + qr + kvr + dims:5 + qr + kvr + rd])
+    # the same rows given as three split sums (float32), with the columns behind them as a gate
+    parts = rng.normal(size=(3,) + f.shape)
+    parts[2] = fr - parts[0] - parts[1]
+    line2 = latent_line(2, 128, kvr + rd, t, seed=4)
+    cq2 = torch.empty((T, qr), dtype=t, device=DEV)
+    gate = torch.empty((T, 3), dtype=t, device=DEV)
+    K.latent_prep(None, 5, 5 + qr, qr, kvr, rd, dev(wq, t), dev(wkv, t), 1e-5, dev(freqs), dims,
+                  amp, step, line2, cq2, True, partial=dev(parts), gate_out=gate,
+                  gate_col=5 + qr + kvr + rd)
+    assert np.abs(cq2.float().cpu().numpy() - want_q).max() < tol * np.abs(want_q).max()
+    assert np.abs(gate.float().cpu().numpy() - fr[:, -3:]).max() < tol * np.abs(fr).max()
+    for i in range(T):
+        want = np.concatenate([want_c[i], want_r[i]])
+        assert np.abs(read_row(line2, slot[i], int(pos[i])) - want).max() < tol * np.abs(want).max(), i
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -444,11 +458,29 @@ def test_router_kernel_ties_and_weights():
     ids = torch.empty((2, 2), dtype=torch.int32, device=DEV)
     w = torch.empty((2, 2), dtype=torch.float32, device=DEV)
     sg = torch.empty((2,), dtype=torch.float32, device=DEV)
-    K.moe_route(z, 4, 2, 4, ids, w, sg)                       # column 4 is the shared gate's
-    assert ids.cpu().tolist() == [[1, 2], [3, 0]]             # the lower index on a tie
     want = np.exp([0.0, -0.5]) / np.exp([0.0, -0.5]).sum()
-    assert np.allclose(w.cpu().numpy(), [[0.5, 0.5], want], atol=1e-6)
-    assert np.allclose(sg.cpu().numpy(), plain.sigmoid(np.array([9.0, -2.0])), atol=1e-6)
+
+    def check_choice():
+        assert ids.cpu().tolist() == [[1, 2], [3, 0]]         # the lower index on a tie
+        assert np.allclose(w.cpu().numpy(), [[0.5, 0.5], want], atol=1e-6)
+        assert np.allclose(sg.cpu().numpy(), plain.sigmoid(np.array([9.0, -2.0])), atol=1e-6)
+
+    K.moe_route(z, 4, 2, 4, ids, w, sg)                       # column 4 is the shared gate's
+    check_choice()
+    # the logits as two split sums (exact in float32), and choice and lists in one kernel
+    halves = torch.stack([z * 0.25, z * 0.75]).contiguous()
+    ids.zero_(), w.zero_(), sg.zero_()
+    K.moe_route(halves, 4, 2, 4, ids, w, sg)
+    check_choice()
+    ids.zero_(), w.zero_(), sg.zero_()
+    max_tiles = 1 + 4
+    plan = torch.full((2 + 4 + 4 + 2 * max_tiles,), -7, dtype=torch.int32, device=DEV)
+    K.moe_route_plan(halves, 4, 2, 4, ids, w, sg, 8, max_tiles, plan)
+    check_choice()
+    got = plan.cpu().tolist()
+    assert got[0] == 4                                        # experts 0, 1, 2, 3: a tile each
+    assert got[1:6] == [0, 1, 2, 3, 4]                        # where each expert's list begins
+    assert sorted(got[6:10]) == [0, 1, 2, 3] and got[6:10][0] == 3    # expert 0 was chosen by a = 3
 
 
 # ---------------------------------------------------------------------------- the engine
