@@ -200,6 +200,22 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// The sum over the split sums of one element: p[0] + p[stride] + ... (parts of them), added in
+// that order, with up to eight loads in flight at once (a loop of dependent loads would wait a
+// trip to memory for each).
+__device__ __forceinline__ float sum_parts(const float* __restrict__ p, int parts, size_t stride) {
+  float v = 0.f;
+  for (int p0 = 0; p0 < parts; p0 += 8) {
+    float a[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = p0 + j < parts ? p[(size_t)(p0 + j) * stride] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (p0 + j < parts) v = (p0 + j == 0) ? a[j] : v + a[j];
+  }
+  return v;
+}
+
 // Sum over a block of up to 1024 threads; every thread gets the result. `red` holds 33 floats.
 __device__ __forceinline__ float block_sum(float v, float* red) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

@@ -318,7 +318,7 @@ __global__ void dynamic_tanh_kernel(float* __restrict__ x, const float* __restri
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     float v = xr[c];
     if (parts > 0) {
-      for (int p = 0; p < parts; ++p) v += partial[p * part_stride + (size_t)src * H + c];
+      v += sum_parts(partial + (size_t)src * H + c, parts, part_stride);
       if (!xb) xr[c] = v;
     }
     if (xb) xr[c] = v + to_f32<TW>(xb[c]);

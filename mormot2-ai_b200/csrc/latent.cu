@@ -47,7 +47,7 @@ __device__ __forceinline__ float rotated(const float* buf, int i, int rot_dims,
 // the product that made them, added up here in split order) instead of f, and gate_n further
 // columns from gate_col on are added up too and written to gate_out [T, gate_n].
 template <typename T, typename TW>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 latent_prep_kernel(const T* __restrict__ f, int ld, int q_col, int kv_col, int q_rank, int kv_rank,
                    int rot_dim, const TW* __restrict__ w_q, const TW* __restrict__ w_kv, float eps,
                    const float* __restrict__ inv_freq, int rot_dims, float amplitude,
@@ -65,9 +65,7 @@ latent_prep_kernel(const T* __restrict__ f, int ld, int q_col, int kv_col, int q
   const float* prow = partial + (size_t)t * ld;
   auto value = [&](int col) -> float {
     if (parts == 0) return to_f32<T>(row[col]);
-    float v = prow[col];
-    for (int p = 1; p < parts; ++p) v += prow[p * part_stride + col];
-    return v;
+    return sum_parts(prow + col, parts, part_stride);
   };
   float* bq = buf;
   float* bc = buf + q_rank;
@@ -123,7 +121,8 @@ MB_EXPORT int mb_latent_prep(const void* f, int dtype, int ld, int q_col, int kv
   const size_t smem = (size_t)(q_rank + kv_rank + rot_dim) * sizeof(float);
   if (smem > 48 * 1024) MB_FAIL("mb_latent_prep: latents of %d values", q_rank + kv_rank + rot_dim);
 #define GO(T_, TW_)                                                                          \
-  mb_launch(latent_prep_kernel<T_, TW_>, dim3(T), dim3(128), smem, s, (const T_*)f, ld, q_col, \
+  mb_launch(latent_prep_kernel<T_, TW_>, dim3(T), dim3(parts > 0 ? 512 : 128), smem, s,      \
+            (const T_*)f, ld, q_col,                                                          \
             kv_col, q_rank, kv_rank, rot_dim, (const TW_*)w_q, (const TW_*)w_kv, eps, inv_freq, \
             rot_dims, amplitude, tok_slot, tok_pos, page_table, max_pages, ring_pages,       \
             (T_*)pool, (T_*)cq_out, write_cache, partial, parts, (size_t)part_stride,        \

@@ -26,9 +26,7 @@ MB_DEFINE_LAST_ERROR
 // (or -1) the shared expert's gate logit. One warp per token.
 __device__ __forceinline__ float route_logit(const float* __restrict__ zr, int parts,
                                              size_t part_stride, int i) {
-  float v = zr[i];
-  for (int p = 1; p < parts; ++p) v += zr[p * part_stride + i];
-  return v;
+  return parts == 1 ? zr[i] : sum_parts(zr + i, parts, part_stride);
 }
 
 __device__ __forceinline__ void route_token(const float* __restrict__ zr, int parts,
@@ -38,15 +36,38 @@ __device__ __forceinline__ void route_token(const float* __restrict__ zr, int pa
   float last_v = INFINITY;
   int last_i = -1;
   float first = 0.f, sum = 0.f, mine = 0.f;  // lane k keeps the k-th chosen logit
+  // up to 256 experts: a lane adds its logits' split sums up once and keeps them
+  const bool kept = E <= 256;
+  float zl[8];
+  if (kept) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = lane + 32 * j;
+      zl[j] = i < E ? route_logit(zr, parts, part_stride, i) : -INFINITY;
+    }
+  }
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    for (int i = lane; i < E; i += 32) {
-      const float v = route_logit(zr, parts, part_stride, i);
-      const bool open = v < last_v || (v == last_v && i > last_i);
-      if (open && (v > best || (v == best && i < best_i))) {
-        best = v;
-        best_i = i;
+    if (kept) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int i = lane + 32 * j;
+        const float v = zl[j];
+        const bool open = i < E && (v < last_v || (v == last_v && i > last_i));
+        if (open && (v > best || (v == best && i < best_i))) {
+          best = v;
+          best_i = i;
+        }
+      }
+    } else {
+      for (int i = lane; i < E; i += 32) {
+        const float v = route_logit(zr, parts, part_stride, i);
+        const bool open = v < last_v || (v == last_v && i > last_i);
+        if (open && (v > best || (v == best && i < best_i))) {
+          best = v;
+          best_i = i;
+        }
       }
     }
 #pragma unroll
@@ -505,9 +526,7 @@ __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restric
     float v = 0.f;
     for (int k = 0; k < top; ++k) v += y[((size_t)t * top + k) * H + c];
     if (shared) {
-      float sh = shared[(size_t)t * H + c];
-      for (int p = 1; p < parts; ++p) sh += shared[p * part_stride + (size_t)t * H + c];
-      v = fmaf(g, sh, v);
+      v = fmaf(g, sum_parts(shared + (size_t)t * H + c, parts, part_stride), v);
     }
     x[(size_t)t * H + c] += v;
   }
