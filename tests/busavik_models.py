@@ -59,9 +59,9 @@ SMALL = {
         "architecture": "Busavik", "vocab": 320, "width": 128, "norm": {"eps": 1e-6},
         "logit_scale": 2.0, "loop": {"start": 1, "stop": 3, "times": 3},
         "layers": [
-            _layer(_mixer(8, 16, 16, 32, 48, 64, 0.18, 1e6, scaling=(8.0, 96, 32.0, 1.0)),
+            _layer(_mixer(8, 16, 16, 32, 48, 64, 0.18, 2e5, scaling=(6.0, 96, 24.0, 1.5)),
                    {"kind": "dense", "ff": 192}),
-            _layer(_mixer(8, 16, 16, 32, 48, 64, 0.18, 1e6, scaling=(8.0, 96, 32.0, 1.0)),
+            _layer(_mixer(8, 16, 16, 32, 48, 64, 0.18, 2e5, scaling=(6.0, 96, 24.0, 1.5)),
                    _moe(64, 16, 4, 96)),
             _layer(_mixer(4, 32, 32, 16, 80, 48, 0.125, 1e4, scaling=(2.0, 32, 8.0, 2.0)),
                    {"kind": "dense", "ff": 160}),

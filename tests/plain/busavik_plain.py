@@ -132,8 +132,8 @@ class Routing:
     """What a test wants to know of the routers' choices, or to settle about them.
 
     ``margins[(run, t)]``: how far the last chosen logit of token t in layer run ``run`` lies
-    above the first one left out, in units of the spread (standard deviation) of the token's
-    logits. ``forced[(run, t)]``: experts that another implementation chose there; they
+    above the first one left out, in units of the root mean square of the token's logits
+    (their scale; their spread around the mean says nothing when there are two or three). ``forced[(run, t)]``: experts that another implementation chose there; they
     replace the plain choice where the two differ and the margin is below ``close`` (a
     computation in 16 bits may fall on either side of such a call), and where the margin is
     larger the difference is an error."""
@@ -152,7 +152,8 @@ def moe_ff(h, mlp: Dict, W, prefix: str, routing: Optional[Routing] = None, run:
     if routing is not None:
         for t in range(h.shape[0]):
             zs = np.sort(z[t])[::-1]
-            margin = (zs[top - 1] - zs[top]) / max(z[t].std(), 1e-30) if top < len(zs) else np.inf
+            scale = max(float(np.sqrt(np.mean(z[t] ** 2))), 1e-30)
+            margin = (zs[top - 1] - zs[top]) / scale if top < len(zs) else np.inf
             routing.margins[(run, t)] = float(margin)
             theirs = routing.forced.get((run, t))
             if theirs is not None and set(int(e) for e in theirs) != set(chosen[t].tolist()):
