@@ -67,22 +67,29 @@ class GroupPlan:
     max_pages: int      # entries of a sequence's page-table row
     ring_pages: int
     planes: int = 2     # 2: keys and values; 1: one row per token (a latent)
+    v_dim: int = 0      # the size of a value row where it differs from head_dim (0: the same)
 
 
 def plan_groups(needs: Dict[int, Tuple[int, int, int]], max_tokens: int, max_context: int,
                 max_slots: int, chunk: int) -> List[GroupPlan]:
-    """Groups the lines by (kv_heads, head_dim, window, planes) and sizes each group's pool.
+    """Groups the lines by (kv_heads, head_dim, window, planes, v_dim) and sizes each group's
+    pool.
 
-    ``needs[line] = (kv_heads, head_dim, window)`` or ``(kv_heads, head_dim, window, planes)``; ``max_tokens`` is the most tokens that live
+    ``needs[line] = (kv_heads, head_dim, window)``, ``(kv_heads, head_dim, window, planes)`` or
+    ``(kv_heads, head_dim, window, planes, v_dim)``; ``max_tokens`` is the most tokens that live
     sequences hold together (each rounded up to whole pages); ``chunk`` is the most new
     positions of one sequence in one pass of the model.
     """
     total_pages = pages_for(max_tokens)
     groups: Dict[Tuple[int, ...], GroupPlan] = {}
     for line in sorted(needs):
-        key = tuple(needs[line]) + (2,) * (4 - len(needs[line]))
+        key = tuple(needs[line])
+        key += (2,) * (4 - len(key))
+        key += (0,) * (5 - len(key))
+        if key[4] == key[1]:
+            key = key[:4] + (0,)
         if key not in groups:
-            kvh, hd, window, planes = key
+            kvh, hd, window, planes, v_dim = key
             full = pages_for(max_context)
             ring = 0
             if window > 0:
@@ -93,7 +100,7 @@ def plan_groups(needs: Dict[int, Tuple[int, int, int]], max_tokens: int, max_con
                     ring = span
             per_seq = ring if ring else full
             groups[key] = GroupPlan(kvh, hd, window, [], min(total_pages, max_slots * per_seq),
-                                    per_seq, ring, planes)
+                                    per_seq, ring, planes, v_dim)
         groups[key].lines.append(line)
     return list(groups.values())
 

@@ -29,6 +29,7 @@ class CacheLine:
     window: int
     kv_heads: int
     head_dim: int
+    v_dim: int = 0             # the size of a value row (0: head_dim)
 
 
 class CacheStorage:
@@ -40,11 +41,22 @@ class CacheStorage:
         self.tables: List[torch.Tensor] = []
         self.tables_host: List[torch.Tensor] = []
         self.lines: Dict[int, CacheLine] = {}
+        self.value_pools: Dict[int, torch.Tensor] = {}   # of groups whose value rows differ in size
         for g, plan in enumerate(plans):
-            pool = alloc(guards, f"keys and values of group {g}",
-                         (len(plan.lines), plan.planes, plan.n_pages, plan.kv_heads, PAGE,
-                          plan.head_dim),
-                         dtype, device)
+            v_dim = getattr(plan, "v_dim", 0)
+            if v_dim and plan.planes == 2:
+                # keys and values in pools of their own: [lines, 1, pages, kv_heads, PAGE, size]
+                pool = alloc(guards, f"keys of group {g}",
+                             (len(plan.lines), 1, plan.n_pages, plan.kv_heads, PAGE,
+                              plan.head_dim), dtype, device)
+                self.value_pools[g] = alloc(guards, f"values of group {g}",
+                                            (len(plan.lines), plan.n_pages, plan.kv_heads, PAGE,
+                                             v_dim), dtype, device)
+            else:
+                pool = alloc(guards, f"keys and values of group {g}",
+                             (len(plan.lines), plan.planes, plan.n_pages, plan.kv_heads, PAGE,
+                              plan.head_dim),
+                             dtype, device)
             table = alloc(guards, f"page table of group {g}", (max_slots, plan.max_pages),
                           torch.int32, device)
             # pageable on purpose: the copy to the device then reads it before returning, so the
@@ -54,10 +66,13 @@ class CacheStorage:
             self.tables.append(table)
             self.tables_host.append(host)
             for i, line in enumerate(plan.lines):
-                self.lines[line] = CacheLine(pool[i, 0], pool[i, 1] if plan.planes > 1 else None,
-                                             table, plan.max_pages,
+                if g in self.value_pools:
+                    values = self.value_pools[g][i]
+                else:
+                    values = pool[i, 1] if plan.planes > 1 else None
+                self.lines[line] = CacheLine(pool[i, 0], values, table, plan.max_pages,
                                              plan.ring_pages, plan.window, plan.kv_heads,
-                                             plan.head_dim)
+                                             plan.head_dim, v_dim)
         # fixed-size state per slot, at its initial value when a sequence starts; beside it a
         # copy of the same size that a step saves the slots it touches into, so that a step
         # that fails half way leaves the state it found
@@ -71,6 +86,7 @@ class CacheStorage:
 
     def bytes(self) -> int:
         return (sum(p.numel() * p.element_size() for p in self.pools)
+                + sum(p.numel() * p.element_size() for p in self.value_pools.values())
                 + sum(2 * s.numel() * s.element_size() for s in self.states.values()))
 
     def map_pages(self, new_entries: List[List[Tuple[int, int, int]]]) -> None:

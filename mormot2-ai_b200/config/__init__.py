@@ -2,11 +2,13 @@
 from .spec import LayerSpec, ModelSpec, PartSpec, Run
 from .qwen3 import Qwen3Config
 from .busavik import BusavikConfig
+from .fimudra import FimudraConfig
 from .registry import (architectures, config_of_folder, family_of, read_config_json,
                        register_architecture)
 
 register_architecture(Qwen3Config, Qwen3Config.ARCHITECTURE, Qwen3Config.MODEL_TYPE)
 register_architecture(BusavikConfig, BusavikConfig.ARCHITECTURE, BusavikConfig.MODEL_TYPE)
+register_architecture(FimudraConfig, FimudraConfig.ARCHITECTURE, FimudraConfig.MODEL_TYPE)
 
-__all__ = ["LayerSpec", "ModelSpec", "PartSpec", "Run", "Qwen3Config", "BusavikConfig", "architectures",
+__all__ = ["LayerSpec", "ModelSpec", "PartSpec", "Run", "Qwen3Config", "BusavikConfig", "FimudraConfig", "architectures",
            "config_of_folder", "family_of", "read_config_json", "register_architecture"]

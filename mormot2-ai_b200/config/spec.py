@@ -67,6 +67,7 @@ class ModelSpec:
     schedule: Tuple[Run, ...]
     final_norm: PartSpec           # params: name, eps, size
     head: PartSpec                 # params: name, tied
+    streams: int = 0               # > 0: the residual is that many streams [streams, T, hidden]
 
     def cache_lines(self) -> int:
         lines = [r.cache_line for r in self.schedule if r.cache_line is not None]

@@ -24,7 +24,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
                       const int* __restrict__ page_table, int max_pages, int ring_pages,
                       const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                       const int* __restrict__ seq_slot, int nh, int nkv, int hd, int window,
-                      float scale) {
+                      float scale, int vd, const float* __restrict__ sink) {
   extern __shared__ __align__(16) float qs[];  // ATT_WARPS x hd
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -40,7 +40,9 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
 
   int lo = 0;
   if (window > 0 && pos + 1 > window) lo = pos + 1 - window;
-  float m = -INFINITY, l = 0.f;
+  // a sink: one more term exp(sink[h]) in the denominator, as a key of that score (not
+  // scaled) whose value is zero
+  float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
   // VEC: values 4 * lane .. + 3 of every 128; else values lane, lane + 32, ...
   float acc[ATT_MAX_D];
 #pragma unroll
@@ -77,12 +79,12 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const unsigned lo32 = __shfl_sync(0xffffffffu, (unsigned)(row & 0xffffffffu), j);
       const unsigned hi32 = __shfl_sync(0xffffffffu, (unsigned)(row >> 32), j);
-      const T* vr = vpool + (((size_t)hi32 << 32) | lo32) * hd;
+      const T* vr = vpool + (((size_t)hi32 << 32) | lo32) * vd;
       if (VEC) {
 #pragma unroll
         for (int d = 0; d < ATT_MAX_D / 4; ++d) {
           const int i = 4 * lane + 128 * d;
-          if (i < hd) {
+          if (i < vd) {
             const float4 vv = load4<T>(vr + i);
             acc[4 * d] = fmaf(pj, vv.x, acc[4 * d]);
             acc[4 * d + 1] = fmaf(pj, vv.y, acc[4 * d + 1]);
@@ -94,18 +96,18 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
 #pragma unroll
         for (int d = 0; d < ATT_MAX_D; ++d) {
           const int i = lane + 32 * d;
-          if (i < hd) acc[d] = fmaf(pj, to_f32<T>(vr[i]), acc[d]);
+          if (i < vd) acc[d] = fmaf(pj, to_f32<T>(vr[i]), acc[d]);
         }
       }
     }
   }
   const float inv = 1.0f / l;
-  T* op = out + (size_t)t * out_stride + (size_t)h * hd;
+  T* op = out + (size_t)t * out_stride + (size_t)h * vd;
   if (VEC) {
 #pragma unroll
     for (int d = 0; d < ATT_MAX_D / 4; ++d) {
       const int i = 4 * lane + 128 * d;
-      if (i < hd)
+      if (i < vd)
         store4<T>(op + i, make_float4(acc[4 * d] * inv, acc[4 * d + 1] * inv, acc[4 * d + 2] * inv,
                                       acc[4 * d + 3] * inv));
     }
@@ -113,7 +115,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
 #pragma unroll
     for (int d = 0; d < ATT_MAX_D; ++d) {
       const int i = lane + 32 * d;
-      if (i < hd) op[i] = from_f32<T>(acc[d] * inv);
+      if (i < vd) op[i] = from_f32<T>(acc[d] * inv);
     }
   }
 }
@@ -130,13 +132,13 @@ attention_shared_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
                         const int* __restrict__ page_table, int max_pages, int ring_pages,
                         const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                         const int* __restrict__ seq_slot, int nh, int nkv, int hd, int window,
-                        float scale) {
+                        float scale, int vd, const float* __restrict__ sink) {
   extern __shared__ __align__(16) float sm[];
-  const int pitch = hd + 4, pieces = hd / 4;
+  const int pitch = hd + 4, pieces = hd / 4, vpitch = vd + 4, vpieces = vd / 4;
   float* qs = sm;                                  // [ATT_WARPS][hd]
   float* ks = qs + ATT_WARPS * hd;                 // [32][pitch]
-  float* vs = ks + 32 * pitch;                     // [32][pitch]
-  size_t* rows = (size_t*)(vs + 32 * pitch);       // [32] pool rows of the tile's keys
+  float* vs = ks + 32 * pitch;                     // [32][vpitch]
+  size_t* rows = (size_t*)(vs + 32 * vpitch);      // [32] pool rows of the tile's keys
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const int h = blockIdx.y * ATT_WARPS + warp;     // nh is a multiple of ATT_WARPS here
@@ -149,7 +151,7 @@ attention_shared_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
 
   int lo = 0;
   if (window > 0 && pos + 1 > window) lo = pos + 1 - window;
-  float m = -INFINITY, l = 0.f;
+  float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
   float acc[ATT_MAX_D];
 #pragma unroll
   for (int d = 0; d < ATT_MAX_D; ++d) acc[d] = 0.f;
@@ -162,9 +164,11 @@ attention_shared_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
     __syncthreads();
     for (int e = threadIdx.x; e < n * pieces; e += ATT_WARPS * 32) {
       const int key = e / pieces, piece = e - key * pieces;
-      const size_t at = rows[key] * hd + 4 * piece;
-      *(float4*)(ks + key * pitch + 4 * piece) = load4<T>(kpool + at);
-      *(float4*)(vs + key * pitch + 4 * piece) = load4<T>(vpool + at);
+      *(float4*)(ks + key * pitch + 4 * piece) = load4<T>(kpool + rows[key] * hd + 4 * piece);
+    }
+    for (int e = threadIdx.x; e < n * vpieces; e += ATT_WARPS * 32) {
+      const int key = e / vpieces, piece = e - key * vpieces;
+      *(float4*)(vs + key * vpitch + 4 * piece) = load4<T>(vpool + rows[key] * vd + 4 * piece);
     }
     __syncthreads();
     const bool valid = lane < n;
@@ -190,8 +194,8 @@ attention_shared_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
 #pragma unroll
       for (int d = 0; d < ATT_MAX_D / 4; ++d) {
         const int i = 4 * lane + 128 * d;
-        if (i < hd) {
-          const float4 vv = *(const float4*)(vs + j * pitch + i);
+        if (i < vd) {
+          const float4 vv = *(const float4*)(vs + j * vpitch + i);
           acc[4 * d] = fmaf(pj, vv.x, acc[4 * d]);
           acc[4 * d + 1] = fmaf(pj, vv.y, acc[4 * d + 1]);
           acc[4 * d + 2] = fmaf(pj, vv.z, acc[4 * d + 2]);
@@ -201,39 +205,42 @@ attention_shared_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
     }
   }
   const float inv = 1.0f / l;
-  T* op = out + (size_t)t * out_stride + (size_t)h * hd;
+  T* op = out + (size_t)t * out_stride + (size_t)h * vd;
 #pragma unroll
   for (int d = 0; d < ATT_MAX_D / 4; ++d) {
     const int i = 4 * lane + 128 * d;
-    if (i < hd)
+    if (i < vd)
       store4<T>(op + i, make_float4(acc[4 * d] * inv, acc[4 * d + 1] * inv, acc[4 * d + 2] * inv,
                                     acc[4 * d + 3] * inv));
   }
 }
 
 // out[t, h, :] for every token t of the step and head h. q: head h of token t at
-// q + t * q_stride + h * hd (the q part of the fused qkv rows); out likewise with out_stride.
+// q + t * q_stride + h * hd (the q part of the fused qkv rows); out: head h at
+// out + t * out_stride + h * vd. `vd`: the size of a value row (0: hd). `sink`: float32 [nh]
+// or null, one more term exp(sink[h]) in every softmax denominator of head h.
 MB_EXPORT int mb_attention_simt(const void* q, int q_stride, void* out, int out_stride,
                                 const void* kpool, const void* vpool, int dtype,
                                 const int* page_table, int max_pages, int ring_pages,
                                 const int* tok_seq, const int* tok_pos, const int* seq_slot,
                                 int T, int nh, int nkv, int hd, int window, float scale,
-                                void* stream) {
+                                int vd, const float* sink, void* stream) {
   if (T <= 0) return 0;
-  if (hd <= 0 || hd > 32 * ATT_MAX_D)
-    MB_FAIL("mb_attention_simt: heads of %d values are not supported (at most %d)", hd,
-            32 * ATT_MAX_D);
+  if (vd <= 0) vd = hd;
+  if (hd <= 0 || hd > 1024 || vd > 32 * ATT_MAX_D)
+    MB_FAIL("mb_attention_simt: heads of %d and %d values are not supported (at most 1024 "
+            "and %d)", hd, vd, 32 * ATT_MAX_D);
   if (nkv <= 0 || nh % nkv) MB_FAIL("mb_attention_simt: %d heads on %d KV heads", nh, nkv);
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid(T, (nh + ATT_WARPS - 1) / ATT_WARPS);
   const size_t smem = (size_t)ATT_WARPS * hd * sizeof(float);
   // four values with one load: the size of four values divides every row's address
   const int four = dtype == MB_F32 ? 15 : 7;
-  const bool vec = hd % 4 == 0 && q_stride % 4 == 0 && out_stride % 4 == 0 &&
+  const bool vec = hd % 4 == 0 && vd % 4 == 0 && q_stride % 4 == 0 && out_stride % 4 == 0 &&
                    (((uintptr_t)q | (uintptr_t)out | (uintptr_t)kpool | (uintptr_t)vpool) & four) == 0;
   // the four heads of every block share a KV head: the tile goes through shared memory
-  if (vec && (nh / nkv) % ATT_WARPS == 0) {
-    const size_t shared = ((size_t)ATT_WARPS * hd + 2 * 32 * (hd + 4)) * sizeof(float) +
+  if (vec && (nh / nkv) % ATT_WARPS == 0 && hd <= 256) {
+    const size_t shared = ((size_t)ATT_WARPS * hd + 32 * (hd + 4) + 32 * (vd + 4)) * sizeof(float) +
                           32 * sizeof(size_t);
 #define GOS(T_)                                                                               \
   {                                                                                           \
@@ -246,7 +253,7 @@ MB_EXPORT int mb_attention_simt(const void* q, int q_stride, void* out, int out_
     attention_shared_kernel<T_><<<grid, ATT_WARPS * 32, shared, s>>>(                         \
         (const T_*)q, q_stride, (T_*)out, out_stride, (const T_*)kpool, (const T_*)vpool,     \
         page_table, max_pages, ring_pages, tok_seq, tok_pos, seq_slot, nh, nkv, hd, window,   \
-        scale);                                                                               \
+        scale, vd, sink);                                                                     \
   }
     if (dtype == MB_F32) GOS(float) else GOS(__nv_bfloat16)
 #undef GOS
@@ -255,7 +262,8 @@ MB_EXPORT int mb_attention_simt(const void* q, int q_stride, void* out, int out_
 #define GO(T_, V_)                                                                            \
   attention_simt_kernel<T_, V_><<<grid, ATT_WARPS * 32, smem, s>>>(                           \
       (const T_*)q, q_stride, (T_*)out, out_stride, (const T_*)kpool, (const T_*)vpool,       \
-      page_table, max_pages, ring_pages, tok_seq, tok_pos, seq_slot, nh, nkv, hd, window, scale)
+      page_table, max_pages, ring_pages, tok_seq, tok_pos, seq_slot, nh, nkv, hd, window, scale, \
+      vd, sink)
   if (dtype == MB_F32) {
     if (vec) GO(float, true); else GO(float, false);
   } else {

@@ -50,6 +50,8 @@ SOURCES = {
     "latent": "latent.cu",
     "moe": "moe.cu",
     "latent_mma": "latent_mma.cu",
+    "streams": "streams.cu",
+    "recurrent": "recurrent.cu",
 }
 HEADERS = ["common.cuh"]
 EXTRA_HEADERS = {"gemm_tc": ["tc_common.cuh"],

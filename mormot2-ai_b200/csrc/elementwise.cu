@@ -13,7 +13,8 @@ MB_DEFINE_LAST_ERROR
 // ------------------------------------------------------------------ embedding
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ x, int H, int V) {
+                             float* __restrict__ x, int H, int V, float scale, int copies,
+                             size_t copy_stride) {
   mb_grid_wait();
   mb_grid_launch_next();
   const int t = blockIdx.x;
@@ -21,18 +22,26 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
   if (id < 0 || id >= V) id = 0;  // the host refuses such ids before the step
   const TW* row = table + (size_t)id * H;
   float* out = x + (size_t)t * H;
-  for (int c = threadIdx.x; c < H; c += blockDim.x) out[c] = to_f32<TW>(row[c]);
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    const float v = to_f32<TW>(row[c]) * scale;  // times 1 is exact
+    for (int k = 0; k < copies; ++k) out[k * copy_stride + c] = v;
+  }
 }
 
+// x[k][t, :] = table[ids[t], :] * scale for each of `copies` residual streams (copy k starts
+// copy_stride floats after copy k - 1).
 MB_EXPORT int mb_embed(const void* table, int table_dtype, const int* ids, float* x, int T,
-                       int H, int V, void* stream) {
+                       int H, int V, float scale, int copies, long long copy_stride,
+                       void* stream) {
   if (T <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = H >= 1024 ? 256 : 128;
   if (table_dtype == MB_F32)
-    mb_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, s, (const float*)table, ids, x, H, V);
+    mb_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, s, (const float*)table, ids, x, H, V, scale,
+              copies, (size_t)copy_stride);
   else
-    mb_launch(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, s, (const __nv_bfloat16*)table, ids, x, H, V);
+    mb_launch(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, s, (const __nv_bfloat16*)table, ids, x, H, V,
+              scale, copies, (size_t)copy_stride);
   MB_CHECK_LAUNCH("mb_embed");
 }
 
@@ -352,7 +361,7 @@ MB_EXPORT int mb_dynamic_tanh(float* x, const float* partial, int parts, long lo
 // The biases may be null. When `x` is given, the block that handles the first columns of a row
 // also adds `xb` [H] into the float32 residual row x[t, :]: the bias of the product that follows
 // and accumulates onto that row.
-enum { ACT_SILU = 0, ACT_GELU_TANH = 1 };
+enum { ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_CLAMPED_SWISH = 2 };
 __device__ __forceinline__ float act_of(float z, int act) {
   if (act == ACT_GELU_TANH)
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
@@ -362,7 +371,8 @@ __device__ __forceinline__ float act_of(float z, int act) {
 template <typename T, typename TW>
 __global__ void gated_act_kernel(const T* __restrict__ in, T* __restrict__ out, int I, int act,
                                  const TW* __restrict__ bg, const TW* __restrict__ bu,
-                                 float* __restrict__ x, const TW* __restrict__ xb, int H) {
+                                 float* __restrict__ x, const TW* __restrict__ xb, int H,
+                                 float limit) {
   mb_grid_wait();
   mb_grid_launch_next();
   const int t = blockIdx.y;
@@ -371,7 +381,14 @@ __global__ void gated_act_kernel(const T* __restrict__ in, T* __restrict__ out, 
     float g = to_f32<T>(row[c]), u = to_f32<T>(row[I + c]);
     if (bg) g += to_f32<TW>(bg[c]);
     if (bu) u += to_f32<TW>(bu[c]);
-    out[(size_t)t * I + c] = from_f32<T>(act_of(g, act) * u);
+    if (act == ACT_CLAMPED_SWISH) {
+      // g' = min(g, limit), u' = clamp(u, -limit, limit): g' sigmoid(1.702 g') (u' + 1)
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+      out[(size_t)t * I + c] = from_f32<T>(g / (1.0f + expf(-1.702f * g)) * (u + 1.0f));
+    } else {
+      out[(size_t)t * I + c] = from_f32<T>(act_of(g, act) * u);
+    }
   }
   if (x && blockIdx.x == 0)
     for (int c = threadIdx.x; c < H; c += blockDim.x) x[(size_t)t * H + c] += to_f32<TW>(xb[c]);
@@ -379,16 +396,16 @@ __global__ void gated_act_kernel(const T* __restrict__ in, T* __restrict__ out, 
 
 MB_EXPORT int mb_gated_act(const void* in, void* out, int dtype, int T, int I, int act,
                            const void* bg, const void* bu, int b_dtype, float* x, const void* xb,
-                           int H, void* stream) {
+                           int H, float limit, void* stream) {
   if (T <= 0) return 0;
-  if (act != ACT_SILU && act != ACT_GELU_TANH) MB_FAIL("mb_gated_act: activation %d", act);
+  if (act < ACT_SILU || act > ACT_CLAMPED_SWISH) MB_FAIL("mb_gated_act: activation %d", act);
   if ((x == nullptr) != (xb == nullptr)) MB_FAIL("mb_gated_act: x and its bias come together");
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = 256;
   dim3 grid(max(1, min((I + threads - 1) / threads, 64)), T);
 #define GO(T_, TW_)                                                                          \
   mb_launch(gated_act_kernel<T_, TW_>, grid, dim3(threads), 0, s, (const T_*)in, (T_*)out, I, \
-            act, (const TW_*)bg, (const TW_*)bu, x, (const TW_*)xb, H)
+            act, (const TW_*)bg, (const TW_*)bu, x, (const TW_*)xb, H, limit)
   if (dtype == MB_F32) {
     if (b_dtype == MB_F32) GO(float, float); else GO(float, __nv_bfloat16);
   } else {

@@ -95,28 +95,105 @@ __device__ __forceinline__ void route_token(const float* __restrict__ zr, int pa
   if (sg && lane == 0) *sg = 1.0f / (1.0f + expf(-route_logit(zr, parts, part_stride, shared_col)));
 }
 
+// The other scoring: s = softmax(z) over all E columns; the choice goes by s + corr (the lower
+// index on a tie), the weights are the chosen s times wscale, not renormalized. Up to 256
+// columns (a lane keeps eight).
+__device__ __forceinline__ void route_token_scored(const float* __restrict__ zr, int parts,
+                                                   size_t part_stride, int E, int top,
+                                                   const float* __restrict__ corr, float wscale,
+                                                   int* __restrict__ ids, float* __restrict__ w,
+                                                   int lane) {
+  float sc[8], ch[8];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int i = lane + 32 * j;
+    sc[j] = i < E ? route_logit(zr, parts, part_stride, i) : -INFINITY;
+    mx = fmaxf(mx, sc[j]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    sc[j] = lane + 32 * j < E ? expf(sc[j] - mx) : 0.f;
+    sum += sc[j];
+  }
+  sum = warp_sum(sum);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int i = lane + 32 * j;
+    sc[j] = sc[j] / sum;
+    ch[j] = i < E ? sc[j] + (corr ? corr[i] : 0.f) : -INFINITY;
+  }
+  float last_v = INFINITY, mine = 0.f;
+  int last_i = -1;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY, best_s = 0.f;
+    int best_i = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = lane + 32 * j;
+      const float v = ch[j];
+      const bool open = i < E && (v < last_v || (v == last_v && i > last_i));
+      if (open && (v > best || (v == best && i < best_i))) {
+        best = v;
+        best_i = i;
+        best_s = sc[j];
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ov > best || (ov == best && oi < best_i)) {
+        best = ov;
+        best_i = oi;
+        best_s = os;
+      }
+    }
+    if (best_i == 0x7fffffff) {  // nothing left that compares (NaNs): take the next index
+      best_i = min(E - 1, last_i + 1);
+      best_s = 0.f;
+    }
+    if (lane == k) mine = best_s * wscale;
+    if (lane == 0) ids[k] = best_i;
+    last_v = best;
+    last_i = best_i;
+  }
+  if (lane < top) w[lane] = mine;
+}
+
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ z, int ldz, int parts, size_t part_stride, int E,
                  int top, int shared_col, int* __restrict__ ids, float* __restrict__ w,
-                 float* __restrict__ sg, int T) {
+                 float* __restrict__ sg, int T, int mode, const float* __restrict__ corr,
+                 float wscale) {
   mb_grid_wait();
   mb_grid_launch_next();
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T) return;
+  if (mode == 1) {
+    route_token_scored(z + (size_t)t * ldz, parts, part_stride, E, top, corr, wscale,
+                       ids + (size_t)t * top, w + (size_t)t * top, lane);
+    return;
+  }
   route_token(z + (size_t)t * ldz, parts, part_stride, E, top, shared_col, ids + (size_t)t * top,
               w + (size_t)t * top, sg ? sg + t : nullptr, lane);
 }
 
 MB_EXPORT int mb_moe_route(const float* z, int ldz, int parts, long long part_stride, int E,
                            int top, int shared_col, int* ids, float* w, float* sg, int T,
-                           void* stream) {
+                           int mode, const float* corr, float wscale, void* stream) {
   if (T <= 0) return 0;
+  if (mode == 1 && (E > 256 || sg != nullptr))
+    MB_FAIL("mb_moe_route: scores over all of %d columns (at most 256, no gate column)", E);
   if (top <= 0 || top > 32 || top > E) MB_FAIL("mb_moe_route: %d of %d experts", top, E);
   if ((sg != nullptr) != (shared_col >= 0)) MB_FAIL("mb_moe_route: the shared gate and its column");
   if (parts < 1) MB_FAIL("mb_moe_route: %d parts", parts);
   mb_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, (cudaStream_t)stream, z, ldz,
-            parts, (size_t)part_stride, E, top, shared_col, ids, w, sg, T);
+            parts, (size_t)part_stride, E, top, shared_col, ids, w, sg, T, mode, corr, wscale);
   MB_CHECK_LAUNCH("mb_moe_route");
 }
 
@@ -130,15 +207,21 @@ __global__ void __launch_bounds__(1024)
 moe_plan_kernel(int* __restrict__ ids, int A, int E, int bm, int max_tiles,
                 int* __restrict__ plan, const float* __restrict__ z, int ldz, int parts,
                 size_t part_stride, int top, int shared_col, float* __restrict__ w,
-                float* __restrict__ sg) {
+                float* __restrict__ sg, int mode, const float* __restrict__ corr, float wscale,
+                int E_route) {
   mb_grid_wait();
   mb_grid_launch_next();
   extern __shared__ int counts[];  // E counters, then E cursors
   if (z != nullptr) {
     const int T = A / top, lane = threadIdx.x & 31;
-    for (int t = threadIdx.x >> 5; t < T; t += blockDim.x >> 5)
-      route_token(z + (size_t)t * ldz, parts, part_stride, E, top, shared_col,
-                  ids + (size_t)t * top, w + (size_t)t * top, sg ? sg + t : nullptr, lane);
+    for (int t = threadIdx.x >> 5; t < T; t += blockDim.x >> 5) {
+      if (mode == 1)
+        route_token_scored(z + (size_t)t * ldz, parts, part_stride, E_route, top, corr, wscale,
+                           ids + (size_t)t * top, w + (size_t)t * top, lane);
+      else
+        route_token(z + (size_t)t * ldz, parts, part_stride, E_route, top, shared_col,
+                    ids + (size_t)t * top, w + (size_t)t * top, sg ? sg + t : nullptr, lane);
+    }
     __syncthreads();  // the block's own writes of ids are visible to it
   }
   int* cursor = counts + E;
@@ -182,32 +265,43 @@ MB_EXPORT int mb_moe_plan(int* ids, int A, int E, int bm, int max_tiles, int* pl
   if (max_tiles < (A + bm - 1) / bm + E) MB_FAIL("mb_moe_plan: room for %d tiles", max_tiles);
   mb_launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int),
             (cudaStream_t)stream, ids, A, E, bm, max_tiles, plan, (const float*)nullptr, 0, 1,
-            (size_t)0, 1, -1, (float*)nullptr, (float*)nullptr);
+            (size_t)0, 1, -1, (float*)nullptr, (float*)nullptr, 0, (const float*)nullptr, 1.0f, E);
   MB_CHECK_LAUNCH("mb_moe_plan");
 }
 
 // moe_route and moe_plan in one kernel, for a step of at most 64 tokens.
 MB_EXPORT int mb_moe_route_plan(const float* z, int ldz, int parts, long long part_stride, int E,
                                 int top, int shared_col, int* ids, float* w, float* sg, int T,
-                                int bm, int max_tiles, int* plan, void* stream) {
+                                int bm, int max_tiles, int* plan, int mode, const float* corr,
+                                float wscale, int E_route, void* stream) {
   if (T <= 0) return 0;
+  if (E_route < E) MB_FAIL("mb_moe_route_plan: %d routed columns for %d experts", E_route, E);
+  if (mode == 1 && (E_route > 256 || sg != nullptr))
+    MB_FAIL("mb_moe_route_plan: scores over all of %d columns (at most 256, no gate column)", E_route);
   if (T > 64) MB_FAIL("mb_moe_route_plan: %d tokens (at most 64)", T);
-  if (top <= 0 || top > 32 || top > E) MB_FAIL("mb_moe_route_plan: %d of %d experts", top, E);
+  if (top <= 0 || top > 32 || top > E_route) MB_FAIL("mb_moe_route_plan: %d of %d experts", top, E_route);
   if ((sg != nullptr) != (shared_col >= 0)) MB_FAIL("mb_moe_route_plan: the shared gate and its column");
   if (E > 4096 || parts < 1) MB_FAIL("mb_moe_route_plan: %d experts, %d parts", E, parts);
   const int A = T * top;
   if (max_tiles < (A + bm - 1) / bm + E) MB_FAIL("mb_moe_route_plan: room for %d tiles", max_tiles);
   mb_launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int),
             (cudaStream_t)stream, ids, A, E, bm, max_tiles, plan, z, ldz, parts,
-            (size_t)part_stride, top, shared_col, w, sg);
+            (size_t)part_stride, top, shared_col, w, sg, mode, corr, wscale, E_route);
   MB_CHECK_LAUNCH("mb_moe_route_plan");
 }
 
 // ------------------------------------------------------------------ the experts' products
-__device__ __forceinline__ float moe_act(float z, int act) {
+// act(gate) * up. 0: SiLU; 1: the tanh form of GELU; 2: the clamped form
+// g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1).
+__device__ __forceinline__ float moe_gated(float z, float u, int act, float limit) {
+  if (act == 2) {
+    z = fminf(z, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return z / (1.0f + expf(-1.702f * z)) * (u + 1.0f);
+  }
   if (act == 1)
-    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-  return z / (1.0f + expf(-z));
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))) * u;
+  return z / (1.0f + expf(-z)) * u;
 }
 
 #define MG_BN 64
@@ -220,7 +314,7 @@ template <typename T, typename TW, int BM, bool UP>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const T* __restrict__ in, const TW* __restrict__ W, void* __restrict__ out,
                 const int* __restrict__ plan, int A, int E, int max_tiles, int top, int N, int K,
-                int act, const float* __restrict__ weight) {
+                int act, const float* __restrict__ weight, float limit) {
   mb_grid_wait();
   mb_grid_launch_next();
   constexpr int NW = UP ? 2 : 1;
@@ -295,7 +389,7 @@ moe_gemm_kernel(const T* __restrict__ in, const TW* __restrict__ W, void* __rest
       if (gn >= N) continue;
       if (UP) {
         ((T*)out)[(size_t)(r0 + r) * N + gn] =
-            from_f32<T>(moe_act(acc[0][i][j], act) * acc[NW - 1][i][j]);
+            from_f32<T>(moe_gated(acc[0][i][j], acc[NW - 1][i][j], act, limit));
       } else {
         const int a = src[r];
         ((float*)out)[(size_t)a * N + gn] = weight[a] * acc[0][i][j];
@@ -312,7 +406,7 @@ __global__ void __launch_bounds__(MT_THREADS)
 moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ W,
                     void* __restrict__ out, const int* __restrict__ plan, int A, int E,
                     int max_tiles, int top, int N, int K, int act,
-                    const float* __restrict__ weight) {
+                    const float* __restrict__ weight, float limit) {
   mb_grid_wait();
   mb_grid_launch_next();
   constexpr int NB = UP ? 2 : 1;
@@ -345,7 +439,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* _
     if (r >= rows || gn >= N) return;
     if (UP) {
       ((__nv_bfloat16*)out)[(size_t)(r0 + r) * N + gn] =
-          __float2bfloat16_rn(moe_act(acc[0][mi][ni][el], act) * acc[NB - 1][mi][ni][el]);
+          __float2bfloat16_rn(moe_gated(acc[0][mi][ni][el], acc[NB - 1][mi][ni][el], act, limit));
     } else {
       const int a = src[r];
       ((float*)out)[(size_t)a * N + gn] = weight[a] * acc[0][mi][ni][el];
@@ -367,7 +461,7 @@ __global__ void __launch_bounds__(MR_WARPS * 32)
 moe_rows_mma_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ W,
                     void* __restrict__ out, const int* __restrict__ plan, int A, int E,
                     int max_tiles, int top, int N, int K, int act,
-                    const float* __restrict__ weight) {
+                    const float* __restrict__ weight, float limit) {
   mb_grid_wait();
   mb_grid_launch_next();
   constexpr int NB = UP ? 2 : 1;
@@ -441,7 +535,7 @@ moe_rows_mma_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* _
     if (gn >= N || r >= rows) continue;
     if (UP) {
       ((__nv_bfloat16*)out)[(size_t)(r0 + r) * N + gn] =
-          __float2bfloat16_rn(moe_act(acc[0][el], act) * acc[NB - 1][el]);
+          __float2bfloat16_rn(moe_gated(acc[0][el], acc[NB - 1][el], act, limit));
     } else {
       const int a_ = src[r];
       ((float*)out)[(size_t)a_ * N + gn] = weight[a_] * acc[0][el];
@@ -451,7 +545,7 @@ moe_rows_mma_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* _
 
 MB_EXPORT int mb_moe_gemm(const void* in, int dtype, const void* W, int w_dtype, void* out,
                           const int* plan, int A, int E, int max_tiles, int bm, int top, int N,
-                          int K, int up, int act, const float* weight, void* stream) {
+                          int K, int up, int act, const float* weight, float limit, void* stream) {
   if (A <= 0) return 0;
   if (bm != 8 && bm != 16 && bm != 64 && bm != 128) MB_FAIL("mb_moe_gemm: tiles of %d rows", bm);
   if (!up && weight == nullptr) MB_FAIL("mb_moe_gemm: the second product needs the weights");
@@ -474,7 +568,7 @@ MB_EXPORT int mb_moe_gemm(const void* in, int dtype, const void* W, int w_dtype,
     }                                                                                         \
     mb_launch(moe_rows_mma_kernel<UP_>, g8, dim3(MR_WARPS * 32), smem, s,                     \
               (const __nv_bfloat16*)in, (const __nv_bfloat16*)W, out, plan, A, E, max_tiles,  \
-              top, N, K, act, weight);                                                        \
+              top, N, K, act, weight, limit);                                                 \
   }
     if (up) GO8(true) else GO8(false)
 #undef GO8
@@ -487,16 +581,16 @@ MB_EXPORT int mb_moe_gemm(const void* in, int dtype, const void* W, int w_dtype,
     if (up)
       mb_launch(moe_gemm_mma_kernel<true>, dim3((N + 63) / 64, max_tiles), dim3(MT_THREADS), 0, s,
                 (const __nv_bfloat16*)in, (const __nv_bfloat16*)W, out, plan, A, E, max_tiles, top,
-                N, K, act, weight);
+                N, K, act, weight, limit);
     else
       mb_launch(moe_gemm_mma_kernel<false>, dim3((N + 127) / 128, max_tiles), dim3(MT_THREADS), 0,
                 s, (const __nv_bfloat16*)in, (const __nv_bfloat16*)W, out, plan, A, E, max_tiles,
-                top, N, K, act, weight);
+                top, N, K, act, weight, limit);
     MB_CHECK_LAUNCH("mb_moe_gemm");
   }
 #define GO(T_, TW_, BM_, UP_)                                                                \
   mb_launch(moe_gemm_kernel<T_, TW_, BM_, UP_>, grid, dim3(256), 0, s, (const T_*)in,        \
-            (const TW_*)W, out, plan, A, E, max_tiles, top, N, K, act, weight)
+            (const TW_*)W, out, plan, A, E, max_tiles, top, N, K, act, weight, limit)
 #define GO3(T_, TW_)                                                  \
   {                                                                   \
     if (bm == 16) { if (up) GO(T_, TW_, 16, true); else GO(T_, TW_, 16, false); } \
@@ -515,27 +609,47 @@ MB_EXPORT int mb_moe_gemm(const void* in, int dtype, const void* W, int w_dtype,
 // ------------------------------------------------------------------ combine
 // x[t, c] += sum_k y[(t·top + k), c] (k ascending) + sg[t] · shared[t, c]; shared
 // [parts][T, H]: the split sums of the shared expert's last product, added up in split order.
+// An assignment whose expert id is E or more names an identity expert: its term is
+// w[a] · h[t, c] (h: the feed-forward's input, `h_bf16` says of which type). `store`: x = the
+// sum instead of x += it.
 __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ y, int top,
                                    const float* __restrict__ shared, int parts,
-                                   size_t part_stride, const float* __restrict__ sg, int H) {
+                                   size_t part_stride, const float* __restrict__ sg, int H,
+                                   const int* __restrict__ ids, const float* __restrict__ w,
+                                   int E, const void* __restrict__ h, int h_bf16, int store) {
   mb_grid_wait();
   mb_grid_launch_next();
   const int t = blockIdx.x;
   const float g = sg ? sg[t] : 1.0f;
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     float v = 0.f;
-    for (int k = 0; k < top; ++k) v += y[((size_t)t * top + k) * H + c];
+    for (int k = 0; k < top; ++k) {
+      const size_t a = (size_t)t * top + k;
+      if (ids != nullptr && ids[a] >= E) {
+        const float hv = h_bf16 ? __bfloat162float(((const __nv_bfloat16*)h)[(size_t)t * H + c])
+                                : ((const float*)h)[(size_t)t * H + c];
+        v = fmaf(w[a], hv, v);
+      } else {
+        v += y[a * H + c];
+      }
+    }
     if (shared) {
       v = fmaf(g, sum_parts(shared + (size_t)t * H + c, parts, part_stride), v);
     }
-    x[(size_t)t * H + c] += v;
+    if (store) x[(size_t)t * H + c] = v;
+    else x[(size_t)t * H + c] += v;
   }
 }
 
 MB_EXPORT int mb_moe_combine(float* x, const float* y, int top, const float* shared, int parts,
-                             long long part_stride, const float* sg, int T, int H, void* stream) {
+                             long long part_stride, const float* sg, int T, int H,
+                             const int* ids, const float* w, int E, const void* h, int h_dtype,
+                             int store, void* stream) {
   if (T <= 0) return 0;
+  if (ids != nullptr && (w == nullptr || h == nullptr))
+    MB_FAIL("mb_moe_combine: identity experts need the weights and the input rows");
   mb_launch(moe_combine_kernel, dim3(T), dim3(H >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, x,
-            y, top, shared, parts, (size_t)part_stride, sg, H);
+            y, top, shared, parts, (size_t)part_stride, sg, H, ids, w, E, h,
+            h_dtype == MB_BF16 ? 1 : 0, store);
   MB_CHECK_LAUNCH("mb_moe_combine");
 }

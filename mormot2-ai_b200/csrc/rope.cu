@@ -14,7 +14,8 @@ __device__ __forceinline__ float norm_w(const void* w, int w_bf16, int i) {
   return w_bf16 ? __bfloat162float(((const __nv_bfloat16*)w)[i]) : ((const float*)w)[i];
 }
 
-// qkv [T, (nh + 2 nkv) hd]: q heads, then k heads, then v heads of a token. One warp per
+// qkv [T, (nh + nkv) hd + nkv vd]: q heads, then k heads, then v heads (of vd values each) of a
+// token. One warp per
 // (token, head): RMSNorm over the head with q_norm / k_norm (null: no norm), rotate_half over
 // the first rot_dim values with angle = f32(inv_freq[i] * pos), q written back in place, k and
 // v (when write_kv) stored in the cache at the token's slot and position.
@@ -25,7 +26,7 @@ __global__ void qk_norm_rope_store_kernel(
     const float* __restrict__ inv_freq, int rot_dim, const int* __restrict__ tok_slot,
     const int* __restrict__ tok_pos,
     const int* __restrict__ page_table, int max_pages, int ring_pages, T* __restrict__ kpool,
-    T* __restrict__ vpool, int nh, int nkv, int hd, int write_kv) {
+    T* __restrict__ vpool, int nh, int nkv, int hd, int write_kv, int vd) {
   mb_grid_wait();
   mb_grid_launch_next();
   extern __shared__ float heads[];  // QK_WARPS x hd
@@ -36,18 +37,22 @@ __global__ void qk_norm_rope_store_kernel(
   if (head >= total) return;
   const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
   if (!is_q && !write_kv) return;
-  T* src = qkv + (size_t)t * total * hd + (size_t)head * hd;
+  const size_t width = (size_t)(nh + nkv) * hd + (size_t)nkv * vd;
+  T* src = qkv + (size_t)t * width +
+           (head < nh + nkv ? (size_t)head * hd
+                            : (size_t)(nh + nkv) * hd + (size_t)(head - nh - nkv) * vd);
   float* buf = heads + warp * hd;
   const int pos = tok_pos[t];
   T* dst = src;
   if (!is_q) {
     const int g = is_k ? head - nh : head - nh - nkv;
     const size_t row = kv_row(page_table, max_pages, ring_pages, tok_slot[t], pos, nkv, g);
-    dst = (is_k ? kpool : vpool) + row * hd;
     if (!is_k) {  // values are stored as they are
-      for (int i = lane; i < hd; i += 32) dst[i] = src[i];
+      dst = vpool + row * vd;
+      for (int i = lane; i < vd; i += 32) dst[i] = src[i];
       return;
     }
+    dst = kpool + row * hd;
   }
   const TW* w = is_q ? q_norm : k_norm;
   float sum = 0.f;
@@ -354,8 +359,9 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
                                     const int* tok_slot, const int* tok_pos,
                                     const int* page_table, int max_pages, int ring_pages,
                                     void* kpool, void* vpool, int T, int nh, int nkv, int hd,
-                                    int write_kv, void* stream) {
+                                    int write_kv, int vd, void* stream) {
   if (T <= 0) return 0;
+  if (vd <= 0) vd = hd;
   if (rot_dim < 0 || rot_dim > hd || (rot_dim & 1))
     MB_FAIL("mb_qk_norm_rope_store: %d of %d values rotate", rot_dim, hd);
   if (hd <= 0 || hd > 1024) MB_FAIL("mb_qk_norm_rope_store: heads of %d", hd);
@@ -364,7 +370,7 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
   const bool aligned = !(((uintptr_t)qkv | (uintptr_t)partial | (uintptr_t)q_out |
                           (uintptr_t)kpool | (uintptr_t)vpool) & 15) && (part_stride & 3) == 0;
   const bool fast = dtype == MB_BF16 && rot_dim == hd && (hd == 64 || hd == 128 || hd == 256) &&
-                    aligned;
+                    aligned && vd == hd;
   if ((partial || q_out) && !fast)
     MB_FAIL("mb_qk_norm_rope_store: partial sums or a separate q for heads of %d values "
             "(%d rotate)%s are not supported", hd, rot_dim, aligned ? "" : ", not 16-byte aligned,");
@@ -405,7 +411,7 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
   mb_launch(qk_norm_rope_store_kernel<T_, TW_>, dim3(grid), dim3(QK_WARPS * 32), smem, s,                         \
       (T_*)qkv, (const TW_*)q_norm, (const TW_*)k_norm, eps, inv_freq, rot_dim, tok_slot,      \
       tok_pos, page_table, max_pages, ring_pages, (T_*)kpool, (T_*)vpool, nh, nkv,   \
-      hd, write_kv)
+      hd, write_kv, vd)
   if (dtype == MB_F32 && w_dtype == MB_F32) QK_LAUNCH(float, float);
   else if (dtype == MB_F32) QK_LAUNCH(float, __nv_bfloat16);
   else if (w_dtype == MB_F32) QK_LAUNCH(__nv_bfloat16, float);

@@ -75,7 +75,7 @@ class Engine:
         self.max_step_tokens = max(max_step_tokens, self.max_slots)
         build.compile_libraries(rt.libraries(self.model.parts()))
         self.model.bind(weights, rt)
-        needs = {line: (n.kv_heads, n.head_dim, n.window, n.planes)
+        needs = {line: (n.kv_heads, n.head_dim, n.window, n.planes, n.v_dim)
                  for line, n in self.model.line_needs.items()}
         self.plans = plan_groups(needs, max_tokens, self.max_context, self.max_slots,
                                  self.prefill_chunk)

@@ -29,7 +29,7 @@ class Layer:
                                   feed_forward=self.feed_forward, norms=self.norms)
 
     def parts(self):
-        return [self.mixer, self.feed_forward] + list(self.norms.values())
+        return [self.mixer, self.feed_forward, self.block] + list(self.norms.values())
 
 
 class DecoderModel:
@@ -94,8 +94,9 @@ class DecoderModel:
                     raise ConfigError(f"entry {i} of the order reads cache line {line} "
                                       "before any entry wrote it")
                 have = self.line_needs[line]
-                if ((have.kv_heads, have.head_dim, have.planes)
-                        != (need.kv_heads, need.head_dim, need.planes)):
+                if ((have.kv_heads, have.head_dim, have.planes, have.v_dim or have.head_dim)
+                        != (need.kv_heads, need.head_dim, need.planes,
+                            need.v_dim or need.head_dim)):
                     raise ConfigError(f"entry {i} of the order reads cache line {line} with "
                                       "other head sizes than it was written with")
 
@@ -109,11 +110,15 @@ class DecoderModel:
     def forward(self, step, cache, on_state=None) -> Optional[torch.Tensor]:
         """``cache``: the ``CacheStorage``. ``on_state(name, x)``: called with the residual
         after the embedding and after every entry of the order (for tests)."""
-        x = torch.empty((step.T, self.spec.hidden_size), dtype=torch.float32,
-                        device=self.rt.device)
+        # the residual: [T, hidden], or [streams, T, hidden] for a model of several streams
+        shape = (step.T, self.spec.hidden_size)
+        if self.spec.streams:
+            shape = (self.spec.streams,) + shape
+        x = torch.empty(shape, dtype=torch.float32, device=self.rt.device)
         self.embedding.forward(step.tok_ids, x)
         if on_state:
-            on_state("embed", x)
+            report, on_state = on_state, lambda name, x: report(name, x if x.dim() == 2 else x.sum(0))
+            on_state("embed", x[0] if x.dim() == 3 else x)
         pending = None      # split sums of the last product, not yet added into x
         for i, run in enumerate(self.spec.schedule):
             line = cache.lines.get(run.cache_line) if run.cache_line is not None else None

@@ -157,9 +157,12 @@ class Runtime:
             return
         K.latent_attention(q, out, step, line, nh, kv_rank, rot_dim, window, scale)
 
-    def attention(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale) -> None:
-        if self.fast_kernels:
+    def attention(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale, vd=0,
+                  sink=None) -> None:
+        """``vd``: the size of a value row where it differs from ``hd``; ``sink``: float32
+        [nh], one more term of every softmax denominator."""
+        if self.fast_kernels and (not vd or vd == hd) and sink is None:
             from ..parts import attention_fast
             if attention_fast.run(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale):
                 return
-        K.attention_simt(q, q_stride, out, step, line, nh, nkv, hd, window, scale)
+        K.attention_simt(q, q_stride, out, step, line, nh, nkv, hd, window, scale, vd, sink)

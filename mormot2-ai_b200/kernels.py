@@ -73,7 +73,9 @@ CLASS_OF = {"mb_gemm_tc": "products", "mb_gemm_simt": "products",
             "mb_heads_gemm": "products", "mb_latent_attention": "attention",
             "mb_latent_attention_mma": "attention",
             "mb_moe_route": "routing", "mb_moe_plan": "routing", "mb_moe_route_plan": "routing", "mb_moe_gemm": "products",
-            "mb_moe_combine": "routing"}
+            "mb_moe_combine": "routing", "mb_stream_step": "norms", "mb_add_scaled": "norms",
+            "mb_token_shift": "recurrence", "mb_wkv_scan": "recurrence",
+            "mb_mlstm_scan": "recurrence"}
 
 
 class Timing:
@@ -167,13 +169,16 @@ def _contig(t: torch.Tensor, what: str) -> None:
 
 
 # ------------------------------------------------------------------------------ elementwise
-def embed(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor) -> None:
-    """x[t, :] = table[ids[t], :] as float32."""
-    T, H = x.shape
+def embed(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor, scale: float = 1.0) -> None:
+    """x[t, :] = table[ids[t], :] * scale as float32; x [T, H], or [S, T, H]: S residual
+    streams that all start as the same rows."""
+    copies = x.shape[0] if x.dim() == 3 else 1
+    T, H = x.shape[-2:]
     _contig(table, "the embedding"), _contig(x, "x")
     assert ids.dtype == torch.int32 and x.dtype == torch.float32 and table.shape[1] == H
-    _call("elementwise", "mb_embed", [_vp, _i, _vp, _vp, _i, _i, _i, _vp],
-          _ptr(table), code_of(table.dtype), _ptr(ids), _ptr(x), T, H, table.shape[0], _stream())
+    _call("elementwise", "mb_embed", [_vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _ll, _vp],
+          _ptr(table), code_of(table.dtype), _ptr(ids), _ptr(x), T, H, table.shape[0],
+          float(scale), copies, T * H, _stream())
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: Optional[torch.Tensor],
@@ -217,7 +222,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 
 def qk_norm_rope_store(qkv, q_norm, k_norm, eps, inv_freq, rot_dim, step, line, nh, nkv, hd,
                        write_kv: bool, partial: Optional[torch.Tensor] = None,
-                       q_out: Optional[torch.Tensor] = None) -> None:
+                       q_out: Optional[torch.Tensor] = None, vd: int = 0) -> None:
     """Per-head norm of q and k, rotary positions, q in place (or into ``q_out``), k and v into
     the cache line. ``partial`` [parts, T, width] float32: the split sums of the q/k/v product,
     which stand for ``qkv`` (then None) and are added up here."""
@@ -229,7 +234,8 @@ def qk_norm_rope_store(qkv, q_norm, k_norm, eps, inv_freq, rot_dim, step, line, 
         T, width = qkv.shape
         _contig(qkv, "qkv")
         dtype_code = code_of(qkv.dtype)
-    assert width == (nh + 2 * nkv) * hd
+    vd = vd or hd
+    assert width == (nh + nkv) * hd + nkv * vd
     if rot_dim > 0 and inv_freq is None:
         raise KernelError("a rotary encoding without its frequencies (is the position "
                           "encoding bound?)")
@@ -240,17 +246,18 @@ def qk_norm_rope_store(qkv, q_norm, k_norm, eps, inv_freq, rot_dim, step, line, 
     wd = code_of(q_norm.dtype) if q_norm is not None else F32
     _call("rope", "mb_qk_norm_rope_store",
           [_vp, _vp, _i, _ll, _vp, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _vp, _vp, _i, _i,
-           _vp, _vp, _i, _i, _i, _i, _i, _vp],
+           _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
           _ptr(qkv), _ptr(partial), partial.shape[0] if partial is not None else 0,
           partial.stride(0) if partial is not None else 0, _ptr(q_out), dtype_code,
           _ptr(q_norm), _ptr(k_norm), wd, float(eps),
           _ptr(inv_freq), rot_dim, _ptr(step.tok_slot), _ptr(step.tok_pos),
           _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(line.k), _ptr(line.v),
-          T, nh, nkv, hd, 1 if write_kv else 0, _stream())
+          T, nh, nkv, hd, 1 if write_kv else 0, vd, _stream())
 
 
-ACT_SILU, ACT_GELU_TANH = 0, 1
-ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
+# "clamped_swish": g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1)
+ACT_SILU, ACT_GELU_TANH, ACT_CLAMPED_SWISH = 0, 1, 2
+ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "clamped_swish": ACT_CLAMPED_SWISH}
 
 
 def dynamic_tanh(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, alpha: torch.Tensor,
@@ -287,7 +294,8 @@ def add_bias(x: torch.Tensor, b: torch.Tensor) -> None:
 
 def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: int,
               gate_bias: Optional[torch.Tensor] = None, up_bias: Optional[torch.Tensor] = None,
-              x: Optional[torch.Tensor] = None, x_bias: Optional[torch.Tensor] = None) -> None:
+              x: Optional[torch.Tensor] = None, x_bias: Optional[torch.Tensor] = None,
+              limit: float = 0.0) -> None:
     """out[T, I] = act(gate_up[:, :I] + gate_bias) * (gate_up[:, I:] + up_bias); with ``x`` and
     ``x_bias`` the float32 residual rows also receive that bias (the one of the product that
     is added onto them next)."""
@@ -299,10 +307,10 @@ def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: int,
     if x is not None:
         assert x.dtype == torch.float32 and x.is_contiguous() and x_bias.numel() == x.shape[1]
     _call("elementwise", "mb_gated_act",
-          [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _vp],
+          [_vp, _vp, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _f, _vp],
           _ptr(gate_up), _ptr(out), code_of(out.dtype), T, I, act, _ptr(gate_bias),
           _ptr(up_bias), code_of(biases[0].dtype) if biases else F32, _ptr(x), _ptr(x_bias),
-          x.shape[1] if x is not None else 0, _stream())
+          x.shape[1] if x is not None else 0, float(limit), _stream())
 
 
 def scale_rows(x: torch.Tensor, factor: float) -> None:
@@ -311,6 +319,136 @@ def scale_rows(x: torch.Tensor, factor: float) -> None:
     _contig(x, "x")
     _call("elementwise", "mb_scale", [_vp, _ll, _f, _vp], _ptr(x), x.numel(), float(factor),
           _stream())
+
+
+# ------------------------------------------------------------------------------ residual streams
+def _terms(terms):
+    """[(y [T, H] float32, factor)] as the arrays the kernels take."""
+    n = len(terms)
+    ys = (_vp * n)(*[_ptr(y) for y, _ in terms])
+    fs = (_f * n)(*[float(f) for _, f in terms])
+    for y, _ in terms:
+        assert y.dtype == torch.float32 and y.is_contiguous()
+    return ys, fs, n
+
+
+def stream_step(x: torch.Tensor, update=None, read=None) -> None:
+    """One pass over the residual streams x [S, T, H] (or [T, H]: one stream), float32.
+    ``update = (mix [S, S], out [S], terms)``: x_t <- sum_s mix[s, t] x_s + out[t] y with
+    y = sum_b factor_b y_b over ``terms = [(y_b, factor_b)]``. ``read = (in [S] or None (ones),
+    w [H], eps, out [R, H], rows int32 [R] or None, R)``: the layer norm of u = sum_s in[s] x_s
+    (after the update) times w."""
+    S = x.shape[0] if x.dim() == 3 else 1
+    T, H = x.shape[-2:]
+    _contig(x, "x")
+    assert x.dtype == torch.float32
+    mix = outc = ys = fs = None
+    n = 0
+    if update is not None:
+        mix, outc, terms = update
+        assert mix.dtype == outc.dtype == torch.float32 and mix.numel() == S * S
+        assert outc.numel() == S and mix.is_contiguous()
+        ys, fs, n = _terms(terms)
+        for y, _ in terms:
+            assert y.shape == (T, H)
+    a = w = out = rows = None
+    eps, R = 0.0, T
+    if read is not None:
+        a, w, eps, out, rows, R = read
+        assert a is None or (a.dtype == torch.float32 and a.numel() == S)
+        assert w.numel() == H and out.is_contiguous() and out.shape == (R, H)
+    _call("streams", "mb_stream_step",
+          [_vp, _ll, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _i, _i, _vp],
+          _ptr(x), T * H, S, _ptr(mix), _ptr(outc), ys, fs, n, _ptr(a), _ptr(w),
+          code_of(w.dtype) if w is not None else F32, float(eps), _ptr(out),
+          code_of(out.dtype) if out is not None else F32, _ptr(rows), R, H, _stream())
+
+
+def add_scaled(x: torch.Tensor, terms, store: bool = False) -> None:
+    """x (+)= sum_b factor_b y_b for ``terms = [(y_b, factor_b)]``, all float32 of x's shape."""
+    assert x.dtype == torch.float32
+    _contig(x, "x")
+    ys, fs, n = _terms(terms)
+    for y, _ in terms:
+        assert y.shape == x.shape
+    _call("streams", "mb_add_scaled", [_vp, _vp, _vp, _i, _ll, _i, _vp],
+          _ptr(x), ys, fs, n, x.numel(), 1 if store else 0, _stream())
+
+
+# ------------------------------------------------------------------------------ recurrences
+def token_shift(h: torch.Tensor, state: torch.Tensor, step, mu: torch.Tensor,
+                out: torch.Tensor) -> None:
+    """out[s, t] = h[t] + (h[t-1] - h[t]) * mu[s] for every s; the row before a sequence's
+    first row of this step is read from its state (``state`` [slots, >= W] float32, a view
+    whose rows may lie apart)."""
+    T, W = h.shape
+    n = mu.shape[0]
+    state_off = 0
+    _contig(h, "h"), _contig(out, "out"), _contig(mu, "mu")
+    assert state.stride(1) == 1
+    assert out.shape == (n, T, W) and out.dtype == h.dtype and mu.shape == (n, W)
+    assert mu.dtype == torch.float32 and state.dtype == torch.float32
+    _call("recurrent", "mb_token_shift",
+          [_vp, _i, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp],
+          _ptr(h), code_of(h.dtype), _ptr(state), state.stride(0), state_off, _ptr(step.tok_seq),
+          _ptr(step.seq_start), _ptr(step.seq_slot), _ptr(mu), n, _ptr(out), T, W, _stream())
+
+
+def tanh_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = tanh(x): float32 in, the activation type out."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    assert x.numel() == out.numel()
+    _call("recurrent", "mb_tanh", [_vp, _vp, _i, _ll, _vp], _ptr(x), _ptr(out),
+          code_of(out.dtype), x.numel(), _stream())
+
+
+def wkv_scan(r, k, v, lw, g, w0, u, normw, eps: float, state: torch.Tensor,
+             h: torch.Tensor, step, out: torch.Tensor, heads: int, dim: int) -> None:
+    """The decaying matrix state, token after token (csrc/recurrent.cu). r, k, v, lw, g:
+    float32 [T, >= heads * dim] with one row stride; the state row of a slot holds the last h
+    (``h.shape[1]`` values) and then heads x dim x dim values."""
+    T = out.shape[0]
+    state_off = 0
+    ld = r.stride(0)
+    for t in (r, k, v, lw, g):
+        assert t.dtype == torch.float32 and t.stride(1) == 1 and t.stride(0) == ld
+    for t in (w0, u, normw):
+        assert t.dtype == torch.float32 and t.numel() == heads * dim and t.is_contiguous()
+    _contig(out, "out"), _contig(h, "h")
+    assert out.dtype == h.dtype and out.shape == (T, heads * dim) and state.dtype == torch.float32
+    assert state.stride(1) == 1 and state.shape[1] >= h.shape[1] + heads * dim * dim
+    _call("recurrent", "mb_wkv_scan",
+          [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _f, _vp, _ll, _ll, _vp, _i, _i, _vp, _vp,
+           _vp, _i, _i, _i, _vp],
+          _ptr(r), _ptr(k), _ptr(v), _ptr(lw), _ptr(g), ld, _ptr(w0), _ptr(u), _ptr(normw),
+          float(eps), _ptr(state), state.stride(0), state_off, _ptr(h), code_of(h.dtype),
+          h.shape[1], _ptr(step.seq_start), _ptr(step.seq_slot), _ptr(out), step.B, heads, dim,
+          _stream())
+
+
+def mlstm_scan(z: torch.Tensor, cols, bi, bf, cap: float, q_scale: float, normw, eps: float,
+               state: torch.Tensor, step, out: torch.Tensor, heads: int,
+               dim: int, vdim: int) -> None:
+    """The gated matrix memory, token after token (csrc/recurrent.cu). z: the fused projection
+    [T, ld] float32; ``cols`` = the first columns of q, k, v, the output gate, the input gate
+    and the forget gate in it. The state row of a slot holds, per head, dim x vdim values of
+    the memory, dim of the normalizer and the running maximum."""
+    T = out.shape[0]
+    state_off = 0
+    assert z.dtype == torch.float32 and z.stride(1) == 1 and len(cols) == 6
+    for t in (bi, bf):
+        assert t.dtype == torch.float32 and t.numel() == heads
+    assert normw.dtype == torch.float32 and normw.numel() == heads * vdim
+    _contig(out, "out")
+    assert out.shape == (T, heads * vdim) and state.dtype == torch.float32
+    assert state.stride(1) == 1 and state.shape[1] >= heads * (dim * vdim + dim + 1)
+    _call("recurrent", "mb_mlstm_scan",
+          [_vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _f, _vp, _f, _vp, _ll, _ll, _vp, _vp,
+           _vp, _i, _i, _i, _i, _i, _vp],
+          _ptr(z), z.stride(0), *[int(c) for c in cols], _ptr(bi), _ptr(bf), float(cap),
+          float(q_scale), _ptr(normw), float(eps), _ptr(state), state.stride(0), state_off,
+          _ptr(step.seq_start), _ptr(step.seq_slot), _ptr(out), code_of(out.dtype), step.B,
+          heads, dim, vdim, _stream())
 
 
 # ------------------------------------------------------------------------------ latent attention
@@ -421,16 +559,24 @@ def _parts_of(z: torch.Tensor):
     return z.shape[0], z.stride(0), z.stride(1)
 
 
+ROUTE_SOFTMAX_OF_CHOSEN, ROUTE_SOFTMAX_OF_ALL = 0, 1
+
+
 def moe_route(z: torch.Tensor, experts: int, top: int, shared_col: int, ids: torch.Tensor,
-              w: torch.Tensor, sg: Optional[torch.Tensor]) -> None:
+              w: torch.Tensor, sg: Optional[torch.Tensor], mode: int = 0,
+              correction: Optional[torch.Tensor] = None, scale: float = 1.0) -> None:
     """Per row of z (float32 router logits, [T, N] or the split sums [parts, T, N] of the
     router's product): the ``top`` largest of the first ``experts`` columns into ``ids`` and
     the softmax over them into ``w``; ``sg`` = sigmoid of column ``shared_col``."""
     parts, stride, ldz = _parts_of(z)
     assert ids.dtype == torch.int32 and w.dtype == torch.float32
-    _call("moe", "mb_moe_route", [_vp, _i, _i, _ll, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
+    assert correction is None or (correction.dtype == torch.float32
+                                  and correction.numel() == experts)
+    _call("moe", "mb_moe_route",
+          [_vp, _i, _i, _ll, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _f, _vp],
           _ptr(z), ldz, parts, stride, experts, top, shared_col if sg is not None else -1,
-          _ptr(ids), _ptr(w), _ptr(sg), z.shape[-2], _stream())
+          _ptr(ids), _ptr(w), _ptr(sg), z.shape[-2], mode, _ptr(correction), float(scale),
+          _stream())
 
 
 def moe_plan(ids: torch.Tensor, experts: int, bm: int, max_tiles: int,
@@ -442,20 +588,24 @@ def moe_plan(ids: torch.Tensor, experts: int, bm: int, max_tiles: int,
 
 def moe_route_plan(z: torch.Tensor, experts: int, top: int, shared_col: int, ids: torch.Tensor,
                    w: torch.Tensor, sg: Optional[torch.Tensor], bm: int, max_tiles: int,
-                   plan: torch.Tensor) -> None:
-    """``moe_route`` and ``moe_plan`` as one kernel, for a step of at most 64 tokens."""
+                   plan: torch.Tensor, mode: int = 0, correction: Optional[torch.Tensor] = None,
+                   scale: float = 1.0, routed: Optional[int] = None) -> None:
+    """``moe_route`` and ``moe_plan`` as one kernel, for a step of at most 64 tokens.
+    ``routed``: the columns that the router chooses among (``experts`` of them have lists;
+    those after them are identity experts)."""
     parts, stride, ldz = _parts_of(z)
     assert ids.dtype == torch.int32 and w.dtype == torch.float32
     assert plan.dtype == torch.int32 and plan.numel() >= 2 + experts + ids.numel() + 2 * max_tiles
     _call("moe", "mb_moe_route_plan",
-          [_vp, _i, _i, _ll, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _vp],
+          [_vp, _i, _i, _ll, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp, _f, _i, _vp],
           _ptr(z), ldz, parts, stride, experts, top, shared_col if sg is not None else -1,
-          _ptr(ids), _ptr(w), _ptr(sg), z.shape[-2], bm, max_tiles, _ptr(plan), _stream())
+          _ptr(ids), _ptr(w), _ptr(sg), z.shape[-2], bm, max_tiles, _ptr(plan), mode,
+          _ptr(correction), float(scale), routed if routed is not None else experts, _stream())
 
 
 def moe_gemm(src: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: torch.Tensor,
              assignments: int, max_tiles: int, bm: int, top: int, up: bool, act: int = ACT_SILU,
-             weight: Optional[torch.Tensor] = None) -> None:
+             weight: Optional[torch.Tensor] = None, limit: float = 0.0) -> None:
     """One of the experts' two products over the planned tiles. ``up``: w [E, 2N, K] (gate
     rows, then up rows), rows of ``src`` [T, K] gathered, out [A, N]. Else w [E, N, K], src
     [A, K], out [A, N] float32 at the assignment's own row, times ``weight`` [A]."""
@@ -466,16 +616,20 @@ def moe_gemm(src: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: torch.
     assert src.shape[1] == Kd and out.shape[1] == N
     assert out.dtype == (src.dtype if up else torch.float32)
     _call("moe", "mb_moe_gemm",
-          [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+          [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _f, _vp],
           _ptr(src), code_of(src.dtype), _ptr(w), code_of(w.dtype), _ptr(out), _ptr(plan),
           assignments, E, max_tiles, bm, top, N, Kd, 1 if up else 0, act, _ptr(weight),
-          _stream())
+          float(limit), _stream())
 
 
 def moe_combine(x: torch.Tensor, y: torch.Tensor, top: int, shared: Optional[torch.Tensor],
-                sg: Optional[torch.Tensor]) -> None:
+                sg: Optional[torch.Tensor], ids: Optional[torch.Tensor] = None,
+                w: Optional[torch.Tensor] = None, experts: int = 0,
+                h: Optional[torch.Tensor] = None, store: bool = False) -> None:
     """x[t] += sum_k y[t*top + k] + sg[t] * shared[t] (all float32); ``shared`` [T, H] or the
-    split sums [parts, T, H] of the shared expert's last product."""
+    split sums [parts, T, H] of the shared expert's last product. With ``ids``: an assignment
+    whose expert id is ``experts`` or more is an identity expert and adds w · h[t] instead of
+    its row of y. ``store``: x = the sum."""
     T, H = x.shape
     assert x.dtype == y.dtype == torch.float32 and y.shape == (T * top, H)
     _contig(x, "x"), _contig(y, "y")
@@ -483,8 +637,14 @@ def moe_combine(x: torch.Tensor, y: torch.Tensor, top: int, shared: Optional[tor
     if shared is not None:
         assert shared.shape[-2:] == (T, H) and shared.is_contiguous()
         parts, stride, _ = _parts_of(shared)
-    _call("moe", "mb_moe_combine", [_vp, _vp, _i, _vp, _i, _ll, _vp, _i, _i, _vp],
-          _ptr(x), _ptr(y), top, _ptr(shared), parts, stride, _ptr(sg), T, H, _stream())
+    if ids is not None:
+        assert ids.dtype == torch.int32 and w.dtype == torch.float32 and h.shape == (T, H)
+        _contig(h, "h")
+    _call("moe", "mb_moe_combine",
+          [_vp, _vp, _i, _vp, _i, _ll, _vp, _i, _i, _vp, _vp, _i, _vp, _i, _i, _vp],
+          _ptr(x), _ptr(y), top, _ptr(shared), parts, stride, _ptr(sg), T, H, _ptr(ids), _ptr(w),
+          experts, _ptr(h), code_of(h.dtype) if h is not None else F32, 1 if store else 0,
+          _stream())
 
 
 # ------------------------------------------------------------------------------ products
@@ -505,16 +665,20 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int =
 
 # ------------------------------------------------------------------------------ attention
 def attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh, nkv, hd,
-                   window: int, scale: float) -> None:
+                   window: int, scale: float, vd: int = 0,
+                   sink: Optional[torch.Tensor] = None) -> None:
+    """``vd``: the size of a value row when it differs from ``hd``. ``sink``: float32 [nh],
+    one more term exp(sink[h]) in the softmax denominators of head h."""
     T = out.shape[0]
     _contig(out, "out")
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == nh)
     _call("attention_simt", "mb_attention_simt",
           [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f,
-           _vp],
+           _i, _vp, _vp],
           _ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
           code_of(out.dtype), _ptr(line.page_table), line.max_pages, line.ring_pages,
           _ptr(step.tok_seq), _ptr(step.tok_pos), _ptr(step.seq_slot), T, nh, nkv, hd,
-          window, float(scale), _stream())
+          window, float(scale), vd or hd, _ptr(sink), _stream())
 
 
 # ------------------------------------------------------------------------------ sampling

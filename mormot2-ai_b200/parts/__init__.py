@@ -3,7 +3,7 @@ from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSI
                    CacheNeed, Part, StateNeed, TensorNeed, register_block,
                    register_feed_forward, register_mixer, register_norm, register_position)
 from . import (attention, block, embedding, feedforward, latent_attention, moe, norm,  # noqa: F401
-               position)
+               position, recurrent, side_by_side)
 from .linear import Linear
 
 __all__ = ["BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITIONS",

@@ -3,6 +3,11 @@ RMSNorm of q and k (when the spec names their weights), position encoding, keys 
 into the cache line, causal attention with an optional window, output projection added into
 the residual. The steps are the reference's ``AttentionBlock`` (``decoder.pas:2625-2702``);
 head h reads KV head h div (heads div kv_heads) (``backend.cpu.pas:1253``).
+
+Options that a design may name: ``v_dim``, a value size that differs from the key size (the
+cache then keeps keys and values in pools of their own); ``names["sink"]``, a learned number
+per head whose exponential is one more term of the softmax denominator (a key with that
+score, not scaled, and a value of zero).
 """
 from __future__ import annotations
 
@@ -34,7 +39,12 @@ class GqaAttention(Part):
         if p.get("position") and self.position is None:
             raise ConfigError(f"the mixer names the position encoding \"{p['position']}\", "
                               "which the model does not define")
-        self.qw, self.kvw = self.nh * self.hd, self.nkv * self.hd
+        self.vd = int(p.get("v_dim") or self.hd)
+        self.qw, self.kvw, self.vw = self.nh * self.hd, self.nkv * self.hd, self.nkv * self.vd
+        self.ow = self.nh * self.vd
+        self.sink = None
+
+    can_store = True      # forward(..., store=True) writes its output into x instead of adding
 
     def libraries(self, rt) -> List[str]:
         return rt.attention_libraries()
@@ -43,22 +53,26 @@ class GqaAttention(Part):
         n = self.names
         out = [TensorNeed(n["q"], (self.qw, self.hidden)),
                TensorNeed(n["k"], (self.kvw, self.hidden)),
-               TensorNeed(n["v"], (self.kvw, self.hidden)),
-               TensorNeed(n["o"], (self.hidden, self.qw))]
+               TensorNeed(n["v"], (self.vw, self.hidden)),
+               TensorNeed(n["o"], (self.hidden, self.ow))]
+        if "sink" in n:
+            out.append(TensorNeed(n["sink"], (self.nh,), "bias"))
         if "q_norm" in n:
             out += [TensorNeed(n["q_norm"], (self.hd,), "vector"),
                     TensorNeed(n["k_norm"], (self.hd,), "vector")]
         return out
 
     def cache_need(self) -> CacheNeed:
-        return CacheNeed(self.nkv, self.hd, self.window)
+        return CacheNeed(self.nkv, self.hd, self.window, 2, 0 if self.vd == self.hd else self.vd)
 
     def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
         self.rt = rt
-        if self.hd % 16 or self.hd > 256:
+        plain = self.vd == self.hd and "sink" not in self.names
+        if (plain and (self.hd % 16 or self.hd > 256)) or self.hd > 1024 or self.vd > 256:
             raise KernelError(
-                f"heads of {self.hd} values are not supported by the attention kernels "
-                "(a multiple of 16, at most 256)")
+                f"heads of {self.hd} values (value rows of {self.vd}) are not supported by the "
+                "attention kernels (a multiple of 16, at most 256; with a sink or value rows of "
+                "their own size any size up to 1024 and 256)")
         n = self.names
         wq, wk, wv = weights[n["q"]], weights[n["k"]], weights[n["v"]]
         if wq.dtype == wk.dtype == wv.dtype:
@@ -79,19 +93,23 @@ class GqaAttention(Part):
         self.o = Linear(weights[n["o"]], rt)
         self.q_norm = weights.get(n.get("q_norm", ""))
         self.k_norm = weights.get(n.get("k_norm", ""))
+        if "sink" in n:
+            self.sink = weights[n["sink"]].to(torch.float32).contiguous()
 
-    def forward(self, h, x, step, line, state, writes_cache: bool):
+    def forward(self, h, x, step, line, state, writes_cache: bool, store: bool = False):
         """Adds the mixer's output into x, or returns it as ``Pending`` split sums for the next
-        norm to add (a decode step whose output product splits K)."""
+        norm to add (a decode step whose output product splits K). ``store``: x receives the
+        output instead (nothing is left pending then)."""
         from .linear import Pending
         T = h.shape[0]
         nkv = self.nkv if writes_cache else 0
-        width = self.qw + 2 * nkv * self.hd
+        width = self.qw + nkv * (self.hd + self.vd)
         eps = float(self.head_norm_eps) if self.head_norm_eps is not None else 0.0
         inv_freq, rot_dim = (self.position.frequencies() if self.position is not None
                              else (None, 0))
         split_ok = (writes_cache and self.qkv is not None and rot_dim == self.hd
-                    and self.hd in (64, 128, 256) and self.rt.dtype == torch.bfloat16)
+                    and self.hd in (64, 128, 256) and self.rt.dtype == torch.bfloat16
+                    and self.vd == self.hd)
         qkv = self.qkv(h, defer=True) if split_ok else None
         if isinstance(qkv, Pending):
             # the kernel that norms and rotates q and k adds the split sums up as it reads them
@@ -100,9 +118,8 @@ class GqaAttention(Part):
                                  line, self.nh, nkv, self.hd, True, partial=qkv.partial, q_out=q)
             attn = torch.empty((T, self.qw), dtype=self.rt.dtype, device=h.device)
             self.rt.attention(q, self.qw, attn, step, line, self.nh, self.nkv, self.hd,
-                              self.window, self.scale)
-            out = self.o(attn, add_into=x, defer=True)
-            return out if isinstance(out, Pending) else None
+                              self.window, self.scale, sink=self.sink)
+            return self._project(attn, x, store)
         if qkv is not None:
             pass
         elif not writes_cache:
@@ -115,10 +132,17 @@ class GqaAttention(Part):
             self.split[1](h, out=qkv[:, self.qw:self.qw + self.kvw])
             self.split[2](h, out=qkv[:, self.qw + self.kvw:])
         K.qk_norm_rope_store(qkv, self.q_norm, self.k_norm, eps, inv_freq, rot_dim,
-                             step, line, self.nh, nkv, self.hd, writes_cache)
-        attn = torch.empty((T, self.qw), dtype=self.rt.dtype, device=h.device)
+                             step, line, self.nh, nkv, self.hd, writes_cache, vd=self.vd)
+        attn = torch.empty((T, self.ow), dtype=self.rt.dtype, device=h.device)
         self.rt.attention(qkv, width, attn, step, line, self.nh, self.nkv, self.hd,
-                          self.window, self.scale)
+                          self.window, self.scale, vd=self.vd, sink=self.sink)
+        return self._project(attn, x, store)
+
+    def _project(self, attn, x, store: bool):
+        from .linear import Pending
+        if store:
+            self.o(attn, out=x)
+            return None
         out = self.o(attn, add_into=x, defer=True)
         return out if isinstance(out, Pending) else None
 

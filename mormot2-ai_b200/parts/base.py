@@ -56,11 +56,13 @@ class CacheNeed:
     """Keys and values that a mixer keeps for every token: ``kv_heads`` x ``head_dim`` each;
     ``window`` > 0: only the last ``window`` positions are ever read. ``planes``: 2 for keys
     and values, 1 for a mixer that keeps one row per token and reads keys and values out of
-    it (a latent from which both are formed: ``head_dim`` is then the row's whole size)."""
+    it (a latent from which both are formed: ``head_dim`` is then the row's whole size).
+    ``v_dim``: the size of a value row where it differs from a key row's (0: the same)."""
     kv_heads: int
     head_dim: int
     window: int = 0
     planes: int = 2
+    v_dim: int = 0
 
 
 @dataclass(frozen=True)

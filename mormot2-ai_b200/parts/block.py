@@ -7,10 +7,20 @@ A mixer or feed-forward may hand its output back as ``Pending`` split sums inste
 it into x; the norm that reads x next adds them (one kernel does the sum, the residual add
 and the norm). A block that takes part in this says ``accepts_pending = True``, takes the
 sums that the block before left in ``pending`` and returns its own.
+
+``hyper_connections``: the residual is ``streams`` copies x_1 .. x_S (all the embedding's output
+at first). For each sublayer q with its vectors ``in``, ``out`` [S] and its matrix ``mix``
+[S, S] (indexed from, to): u = Σ_s in[s] x_s; y = sublayer(norm(u));
+x_t ← Σ_s mix[s, t] x_s + out[t] · y for all t at once. The write-back of one sublayer and the
+read (with its layer norm) of the next are one kernel (``csrc/streams.cu``), so a block hands
+its last write-back on as pending, as ``prenorm_residual`` hands on split sums.
 """
 from __future__ import annotations
 
-from .base import BLOCKS, Part
+import torch
+
+from ..errors import ConfigError
+from .base import BLOCKS, Part, TensorNeed
 
 
 class PreNormResidualBlock(Part):
@@ -49,9 +59,102 @@ class PreNormResidualBlock(Part):
 
 
 def settle(x, pending) -> None:
-    """Adds pending split sums into the residual x."""
+    """Adds pending split sums into the residual x (or does what else is pending on it)."""
     from .. import kernels as K
+    if hasattr(pending, "settle"):
+        pending.settle(x)
+        return
     K.add_partials(x, pending.partial)
 
 
+class StreamUpdate:
+    """A write-back into the residual streams that has not happened yet: x_t <- sum_s
+    mix[s, t] x_s + out[t] * sum_b factor_b y_b."""
+
+    def __init__(self, mix, out, terms):
+        self.mix, self.out, self.terms = mix, out, terms
+
+    def as_update(self):
+        return (self.mix, self.out, self.terms)
+
+    def settle(self, x) -> None:
+        from .. import kernels as K
+        K.stream_step(x, update=self.as_update())
+
+
+class HyperConnectionsBlock(Part):
+    capturable = True
+    accepts_pending = True
+
+    def __init__(self, spec, prefix: str = "", mixer=None, feed_forward=None, norms=None):
+        super().__init__(spec, prefix)
+        self.mixer, self.feed_forward, self.norms = mixer, feed_forward, norms
+        self.streams = int(spec.params["streams"])
+        if not 1 <= self.streams <= 8:
+            raise ConfigError(f"{self.streams} residual streams (1 to 8)")
+        self.subs = ["mixer"] + (["feed_forward"] if "feed_forward" in norms else [])
+        self.names = {q: {k: prefix + v for k, v in spec.params["names"][q].items()}
+                      for q in self.subs}
+        for q in self.subs:
+            if not hasattr(norms[q], "eps") or not hasattr(norms[q], "weight"):
+                raise ConfigError("hyper-connections read the streams through a norm with a "
+                                  "weight and an eps (layernorm)")
+
+    def libraries(self, rt):
+        return ["streams"]
+
+    def tensors(self):
+        S = self.streams
+        out = []
+        for q in self.subs:
+            n = self.names[q]
+            out += [TensorNeed(n["in"], (S,), "vector"), TensorNeed(n["out"], (S,), "vector"),
+                    TensorNeed(n["mix"], (S, S), "identity")]
+        return out
+
+    def bind(self, weights, rt) -> None:
+        self.rt = rt
+        self.w = {q: {k: weights[name].to(torch.float32).contiguous()
+                      for k, name in self.names[q].items()} for q in self.subs}
+
+    def _read(self, q, x, pending):
+        from .. import kernels as K
+        norm = self.norms[q]
+        h = torch.empty((x.shape[1], x.shape[2]), dtype=self.rt.dtype, device=x.device)
+        if pending is not None and not isinstance(pending, StreamUpdate):
+            settle(x, pending)
+            pending = None
+        K.stream_step(x, update=pending.as_update() if pending is not None else None,
+                      read=(self.w[q]["in"], norm.weight, norm.eps, h, None, x.shape[1]))
+        return h
+
+    def _sublayer(self, part, h, args, kwargs=None):
+        """The sublayer's output as terms [(y, factor)]."""
+        y = torch.empty((h.shape[0], h.shape[1]), dtype=torch.float32, device=h.device)
+        if getattr(part, "can_store", False):
+            pending = part.forward(h, y, *args, store=True)
+        else:
+            y.zero_()
+            pending = part.forward(h, y, *args)
+        if pending is not None:
+            settle(y, pending)
+        return [(y, 1.0)]
+
+    def forward(self, x, step, line, state, writes_cache: bool, pending=None):
+        if x.dim() != 3 or x.shape[0] != self.streams:
+            raise ConfigError(f"a residual of shape {tuple(x.shape)} for {self.streams} streams")
+        h = self._read("mixer", x, pending)
+        if hasattr(self.mixer, "forward_branches"):
+            terms = self.mixer.forward_branches(h, step, line, state, writes_cache)
+        else:
+            terms = self._sublayer(self.mixer, h, (step, line, state, writes_cache))
+        pending = StreamUpdate(self.w["mixer"]["mix"], self.w["mixer"]["out"], terms)
+        if "feed_forward" not in self.subs:
+            return pending
+        h = self._read("feed_forward", x, pending)
+        terms = self._sublayer(self.feed_forward, h, (step,))
+        return StreamUpdate(self.w["feed_forward"]["mix"], self.w["feed_forward"]["out"], terms)
+
+
 BLOCKS.register("prenorm_residual", PreNormResidualBlock)
+BLOCKS.register("hyper_connections", HyperConnectionsBlock)

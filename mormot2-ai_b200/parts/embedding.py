@@ -1,5 +1,5 @@
-"""Token embedding (rows of the table into the float32 residual, no scaling:
-``decoder.pas:3292-3309`` of the reference) and the head (logits = h · Headᵀ in float32, the
+"""Token embedding (rows of the table into the float32 residual, times ``scale`` where a
+design names one; the reference scales nothing: ``decoder.pas:3292-3309``) and the head (logits = h · Headᵀ in float32, the
 head being the embedding when tied: ``model.qwen3.pas:555-579``; a head with ``scale``
 multiplies its float32 logits by that constant)."""
 from __future__ import annotations
@@ -20,6 +20,7 @@ class TokenEmbedding(Part):
         super().__init__(spec, prefix)
         self.name = spec.params["name"]
         self.vocab, self.hidden = int(spec.params["vocab_size"]), int(spec.params["hidden_size"])
+        self.scale = float(spec.params.get("scale", 1.0))
 
     def tensors(self) -> List[TensorNeed]:
         return [TensorNeed(self.name, (self.vocab, self.hidden), "table")]
@@ -28,7 +29,8 @@ class TokenEmbedding(Part):
         self.table = weights[self.name]
 
     def forward(self, ids: torch.Tensor, x: torch.Tensor) -> None:
-        K.embed(self.table, ids, x)
+        """x [T, hidden], or [streams, T, hidden]: every stream starts as the same rows."""
+        K.embed(self.table, ids, x, self.scale)
 
 
 class LmHead(Part):

@@ -2,7 +2,10 @@
 sums in float32 (``backend.cpu.pas:1769-1795``, ``ops.cu:116-130`` of the reference).
 
 Dynamic Tanh: y = tanh(alpha · x) · w + b with a learned scalar alpha: a norm that forms no
-mean and no variance, value by value in float32."""
+mean and no variance, value by value in float32.
+
+Layer norm: y = (x − mean) / sqrt(var + eps) · w with the variance as the mean of the squared
+deviations and no bias, in float32. Over a residual of several streams it norms their sum."""
 from __future__ import annotations
 
 from typing import Dict, List, Optional
@@ -80,5 +83,35 @@ class DynamicTanh(Part):
         return out
 
 
+class LayerNorm(Part):
+    capturable = True
+
+    def __init__(self, spec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        self.size = int(spec.params["size"])
+        self.eps = float(spec.params["eps"])
+        self.name = prefix + spec.params["name"]
+        self.weight: Optional[torch.Tensor] = None
+
+    def libraries(self, rt) -> List[str]:
+        return ["streams"]
+
+    def tensors(self) -> List[TensorNeed]:
+        return [TensorNeed(self.name, (self.size,), "vector")]
+
+    def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
+        self.weight = weights[self.name]
+        self.rt = rt
+
+    def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None,
+                n_rows: Optional[int] = None) -> torch.Tensor:
+        """x: the float32 residual [T, size], or [streams, T, size], whose sum is normed."""
+        R = n_rows if n_rows is not None else (rows.numel() if rows is not None else x.shape[-2])
+        out = torch.empty((R, self.size), dtype=self.rt.dtype, device=x.device)
+        K.stream_step(x, read=(None, self.weight, self.eps, out, rows, R))
+        return out
+
+
 NORMS.register("rmsnorm", RmsNorm)
+NORMS.register("layernorm", LayerNorm)
 NORMS.register("dynamic_tanh", DynamicTanh)

@@ -13,6 +13,11 @@ frequency i is f_i · ((1 − ramp_i) + ramp_i / factor): fast-turning pairs kee
 frequency, slow ones are stretched by ``factor``. Cosine and sine are both multiplied by
 ``amplitude`` = 0.1 · ln(factor) + 1. An encoding's ``amplitude`` is 1 unless it says
 otherwise; a mixer passes it to the kernel that rotates.
+
+``rope_scaled_bands`` is the same rotation with the frequencies scaled by wavelength, as
+Llama 3.1 scales them: with the wavelength l = 2π / f, frequencies with l < original / high
+stay, those with l > original / low become f / factor, and between the two, with
+s = (original / l − low) / (high − low), f' = (1 − s) · f / factor + s · f.
 """
 from __future__ import annotations
 
@@ -87,6 +92,34 @@ class RopeYarn(RopeHalf):
             self.slow)).to(rt.device)
 
 
+def banded_inverse_frequencies(theta: float, rot_dim: int, factor: float, low: float,
+                               high: float, original: float) -> np.ndarray:
+    """Float64 arithmetic, rounded to float32 once at the end."""
+    half = rot_dim // 2
+    f = np.exp(-np.log(theta) * 2.0 * np.arange(half, dtype=np.float64) / rot_dim)
+    wavelength = 2.0 * math.pi / f
+    s = (original / wavelength - low) / (high - low) if high != low else np.ones(half)
+    blended = (1.0 - s) * f / factor + s * f
+    out = np.where(wavelength < original / high, f,
+                   np.where(wavelength > original / low, f / factor, blended))
+    return out.astype(np.float32)
+
+
+class RopeScaledBands(RopeHalf):
+    def __init__(self, spec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.factor, self.original = float(p["factor"]), float(p["original"])
+        self.low, self.high = float(p["low"]), float(p["high"])
+        if min(self.factor, self.original, self.low, self.high) <= 0:
+            raise ConfigError("frequency scaling: factor, original, low and high are positive")
+
+    def bind(self, weights, rt) -> None:
+        self.inv_freq = torch.from_numpy(banded_inverse_frequencies(
+            self.theta, self.rot_dim, self.factor, self.low, self.high,
+            self.original)).to(rt.device)
+
+
 class NoPosition(Part):
     capturable = True
     amplitude = 1.0
@@ -97,4 +130,5 @@ class NoPosition(Part):
 
 POSITIONS.register("rope_half", RopeHalf)
 POSITIONS.register("rope_yarn", RopeYarn)
+POSITIONS.register("rope_scaled_bands", RopeScaledBands)
 POSITIONS.register("none", NoPosition)

@@ -1,0 +1,161 @@
+"""Mixers that keep a state of fixed size per sequence instead of keys and values
+(``csrc/recurrent.cu``). The state is float32, starts at zero, is read when a step begins and
+written when it ends; everything that enters the recurrence is float32 on both paths (the
+projections' operands are of the activation type, their sums float32).
+
+``wkv`` — token-shifted time mixing with a decaying matrix state per head. With h' the row
+before (zeros before a sequence's first), each of r, k, v, g, w reads h + (h' − h) · mu_s;
+r, k, v = W_r, W_k, W_v of their mixes (heads × dim), gate = silu(W_g ·), decay
+w = exp(−exp(W_w2 tanh(W_w1 ·) + w0)) per head and key channel;
+o_t = (S + diag(u) k vᵀ)ᵀ r, S ← diag(w) S + k vᵀ; each head's o over its root mean square,
+times ``norm``, times the gate, then W_o. The state is the last h and S.
+
+``mlstm`` — a matrix memory with an exponential input gate and a sigmoid forget gate, both as
+logarithms behind a soft cap c: i = c tanh((W_i h + b_i)/c), f = logsigmoid(c tanh((W_f h + b_f)/c));
+with a running maximum m (from 0): m' = max(f + m, i), S ← e^(f+m−m') S + e^(i−m') k vᵀ, n
+likewise with k, o = Sᵀ q / (max(|n·q|, e^(−m')) + 1e-6) with q scaled by dim^(−1/2); each
+head's o over its root mean square, times ``norm``, times sigmoid(W_g h), then W_o. q, k, v,
+the output gate and both gates are one product.
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .. import kernels as K
+from ..errors import ConfigError
+from .base import MIXERS, Part, StateNeed, TensorNeed
+from .linear import Linear
+
+
+def _f32(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.float32).contiguous()
+
+
+class WkvMixer(Part):
+    capturable = True
+    can_store = True
+    MIXES = ("r", "k", "v", "g", "w")
+
+    def __init__(self, spec, prefix: str = "", positions=None):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.hidden, self.nh, self.dim = int(p["hidden_size"]), int(p["heads"]), int(p["dim"])
+        self.eps = float(p["eps"])
+        # the decay's low rank is a size that only the tensors' shapes give (-1: any)
+        self.rank = int(p.get("decay_rank") or -1)
+        self.names = {k: prefix + v for k, v in p["names"].items()}
+        self.width = self.nh * self.dim
+        if (self.dim * self.dim + 4 * self.dim + 33) * 4 > 200 * 1024:
+            raise ConfigError(f"a decaying state of {self.dim} x {self.dim} values per head is "
+                              "more than the kernel keeps in shared memory")
+
+    def libraries(self, rt) -> List[str]:
+        return ["recurrent"]
+
+    def tensors(self) -> List[TensorNeed]:
+        n, W, HD = self.names, self.hidden, self.width
+        out = [TensorNeed(n["mu_" + s], (W,), "fraction") for s in self.MIXES]
+        out += [TensorNeed(n[s], (HD, W)) for s in ("r", "k", "v", "g")]
+        out += [TensorNeed(n["w1"], (self.rank, W)), TensorNeed(n["w2"], (HD, self.rank)),
+                TensorNeed(n["w0"], (HD,), "bias"), TensorNeed(n["u"], (self.nh, self.dim), "bias"),
+                TensorNeed(n["norm"], (HD,), "vector"), TensorNeed(n["o"], (W, HD))]
+        return out
+
+    def state_need(self) -> StateNeed:
+        return StateNeed((self.hidden + self.nh * self.dim * self.dim,), "float32", 0.0)
+
+    def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
+        self.rt = rt
+        n = self.names
+        self.mu = torch.stack([_f32(weights[n["mu_" + s]]) for s in self.MIXES]).contiguous()
+        self.proj = [Linear(weights[n[s]], rt) for s in ("r", "k", "v", "g")]
+        self.w1, self.w2 = Linear(weights[n["w1"]], rt), Linear(weights[n["w2"]], rt)
+        self.w0, self.u = _f32(weights[n["w0"]]), _f32(weights[n["u"]]).reshape(-1)
+        self.norm = _f32(weights[n["norm"]])
+        self.o = Linear(weights[n["o"]], rt)
+
+    def forward(self, h, x, step, line, state, writes_cache: bool, store: bool = False):
+        T, dev, dt = h.shape[0], h.device, self.rt.dtype
+        mixes = torch.empty((5, T, self.hidden), dtype=dt, device=dev)
+        K.token_shift(h, state, step, self.mu, mixes)
+        z = torch.empty((5, T, self.width), dtype=torch.float32, device=dev)   # r, k, v, g, lw
+        for i, lin in enumerate(self.proj):
+            lin(mixes[i], out=z[i])
+        low = self.w1(mixes[4], out_dtype=torch.float32)
+        low_act = torch.empty(low.shape, dtype=dt, device=dev)
+        K.tanh_rows(low, low_act)
+        self.w2(low_act, out=z[4])
+        y = torch.empty((T, self.width), dtype=dt, device=dev)
+        K.wkv_scan(z[0], z[1], z[2], z[4], z[3], self.w0, self.u, self.norm, self.eps, state, h,
+                   step, y, self.nh, self.dim)
+        if store:
+            self.o(y, out=x)
+        else:
+            self.o(y, add_into=x)
+        return None
+
+
+class MlstmMixer(Part):
+    capturable = True
+    can_store = True
+
+    def __init__(self, spec, prefix: str = "", positions=None):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.hidden, self.nh = int(p["hidden_size"]), int(p["heads"])
+        self.dim, self.vdim = int(p["dim"]), int(p["vdim"])
+        self.cap, self.eps = float(p["gate_cap"]), float(p["eps"])
+        if self.cap <= 0:
+            raise ConfigError(f"a gate cap of {self.cap}")
+        self.names = {k: prefix + v for k, v in p["names"].items()}
+        if (self.dim * self.vdim + 2 * self.dim + 70) * 4 > 200 * 1024:
+            raise ConfigError(f"a matrix memory of {self.dim} x {self.vdim} values per head is "
+                              "more than the kernel keeps in shared memory")
+
+    def libraries(self, rt) -> List[str]:
+        return ["recurrent"]
+
+    def tensors(self) -> List[TensorNeed]:
+        n, W, H = self.names, self.hidden, self.nh
+        return [TensorNeed(n["q"], (H * self.dim, W)), TensorNeed(n["k"], (H * self.dim, W)),
+                TensorNeed(n["v"], (H * self.vdim, W)), TensorNeed(n["g"], (H * self.vdim, W)),
+                TensorNeed(n["i"], (H, W)), TensorNeed(n["f"], (H, W)),
+                TensorNeed(n["i_bias"], (H,), "bias"), TensorNeed(n["f_bias"], (H,), "bias"),
+                TensorNeed(n["norm"], (H * self.vdim,), "vector"),
+                TensorNeed(n["o"], (W, H * self.vdim))]
+
+    def state_need(self) -> StateNeed:
+        return StateNeed((self.nh * (self.dim * self.vdim + self.dim + 1),), "float32", 0.0)
+
+    def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
+        self.rt = rt
+        n = self.names
+        ws = [weights[n[s]] for s in ("q", "k", "v", "g", "i", "f")]
+        if len({w.dtype for w in ws}) > 1:
+            ws = [w.float() for w in ws]
+        self.cols, at = [], 0
+        for w in ws:
+            self.cols.append(at)
+            at += w.shape[0]
+        self.fused = Linear(torch.cat(ws, dim=0), rt)
+        self.bi, self.bf = _f32(weights[n["i_bias"]]), _f32(weights[n["f_bias"]])
+        self.norm = _f32(weights[n["norm"]])
+        self.o = Linear(weights[n["o"]], rt)
+
+    def forward(self, h, x, step, line, state, writes_cache: bool, store: bool = False):
+        T = h.shape[0]
+        z = self.fused(h, out_dtype=torch.float32)
+        y = torch.empty((T, self.nh * self.vdim), dtype=self.rt.dtype, device=h.device)
+        K.mlstm_scan(z, self.cols, self.bi, self.bf, self.cap, self.dim ** -0.5, self.norm,
+                     self.eps, state, step, y, self.nh, self.dim, self.vdim)
+        if store:
+            self.o(y, out=x)
+        else:
+            self.o(y, add_into=x)
+        return None
+
+
+MIXERS.register("wkv", WkvMixer)
+MIXERS.register("mlstm", MlstmMixer)

@@ -1,0 +1,93 @@
+"""Several mixers side by side: all read the same input, and the result is the sum of their
+outputs with a constant factor each. A branch is any registered mixer; at most one of them
+may keep keys and values (it gets the cache line), and the branches' fixed-size states lie one
+after another in the state of this mixer."""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import kernels as K
+from ..config.spec import PartSpec
+from ..errors import ConfigError
+from .base import MIXERS, CacheNeed, Part, StateNeed, TensorNeed
+
+
+class SideBySide(Part):
+    can_store = True
+
+    def __init__(self, spec, prefix: str = "", positions=None):
+        super().__init__(spec, prefix)
+        self.branches, self.scales = [], []
+        for b in spec.params["branches"]:
+            sub = b["mixer"] if isinstance(b["mixer"], PartSpec) else PartSpec(**b["mixer"])
+            self.branches.append(MIXERS.build(sub, prefix, positions=positions))
+            self.scales.append(float(b.get("scale", 1.0)))
+        if not 1 <= len(self.branches) <= 4:
+            raise ConfigError(f"{len(self.branches)} mixers side by side (1 to 4)")
+        if sum(b.cache_need() is not None for b in self.branches) > 1:
+            raise ConfigError("more than one of the mixers side by side keeps keys and values")
+        self.offsets, at = [], 0
+        for b in self.branches:
+            need = b.state_need()
+            n = 0
+            if need is not None:
+                if need.dtype != "float32" or need.init != 0.0 or len(need.shape) != 1:
+                    raise ConfigError("mixers side by side keep flat float32 state that starts at 0")
+                n = int(need.shape[0])
+            self.offsets.append((at, n))
+            at += n
+        self.state_size = at
+
+    @property
+    def capturable(self) -> bool:
+        return all(getattr(b, "capturable", False) for b in self.branches)
+
+    def libraries(self, rt) -> List[str]:
+        out = ["streams"]
+        for b in self.branches:
+            out += [n for n in b.libraries(rt) if n not in out]
+        return out
+
+    def tensors(self) -> List[TensorNeed]:
+        return [t for b in self.branches for t in b.tensors()]
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        for b in self.branches:
+            if b.cache_need() is not None:
+                return b.cache_need()
+        return None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return StateNeed((self.state_size,), "float32", 0.0) if self.state_size else None
+
+    def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
+        self.rt = rt
+        for b in self.branches:
+            b.bind(weights, rt)
+
+    def forward_branches(self, h, step, line, state, writes_cache: bool):
+        """Runs every branch and returns ``[(y_b float32 [T, hidden], factor_b)]``: whoever
+        adds the outputs into the residual does the weighted sum on the way."""
+        terms = []
+        for b, scale, (at, n) in zip(self.branches, self.scales, self.offsets):
+            y = torch.empty((h.shape[0], h.shape[1]), dtype=torch.float32, device=h.device)
+            sub_state = state[:, at:at + n] if n else None
+            sub_line = line if b.cache_need() is not None else None
+            if getattr(b, "can_store", False):
+                pending = b.forward(h, y, step, sub_line, sub_state, writes_cache, store=True)
+            else:
+                y.zero_()
+                pending = b.forward(h, y, step, sub_line, sub_state, writes_cache)
+            if pending is not None:
+                K.add_partials(y, pending.partial)
+            terms.append((y, scale))
+        return terms
+
+    def forward(self, h, x, step, line, state, writes_cache: bool, store: bool = False):
+        K.add_scaled(x, self.forward_branches(h, step, line, state, writes_cache), store)
+        return None
+
+
+MIXERS.register("side_by_side", SideBySide)

@@ -31,7 +31,10 @@ def check_names(needs: Iterable[TensorNeed], source) -> None:
     shapes, types = [], []
     for n in needs:
         if n.name in have:
-            if tuple(source.shape(n.name)) != tuple(n.shape):
+            have_shape = tuple(source.shape(n.name))
+            # a size of -1 is one that only the stored tensor gives
+            if len(have_shape) != len(n.shape) or any(
+                    w != -1 and w != g for w, g in zip(n.shape, have_shape)):
                 shapes.append(f"{n.name} is shaped {list(source.shape(n.name))}, "
                               f"expected {list(n.shape)}")
             dt = source.dtype(n.name)

@@ -2,7 +2,9 @@
 model.safetensors) for tests and traces, or tensors made on the device for benchmarks of
 large shapes.
 
-Matrices and tables are N(0, std), norm weights 1 + N(0, norm_std), drawn in float32 from one
+Matrices, tables and biases are N(0, std), norm weights 1 + N(0, norm_std), fractions (the
+weights of a blend of two rows) uniform in [0, 1), matrices near the identity I + N(0,
+norm_std); drawn in float32 from one
 seeded generator in the order of the tensor names and then rounded to the stored type (the
 reference's fixture tool draws 0.08·randn and 1 + 0.25·randn and rounds to BF16:
 ``tools/infer-ref/make_reference_qwen3.py:837-844`` of the reference project).
@@ -26,6 +28,9 @@ def random_tensors(needs: Iterable[TensorNeed], seed: int, std: float = 0.02,
     gen.manual_seed(seed)
     out: Dict[str, torch.Tensor] = {}
     for n in sorted((n for n in needs if not n.optional), key=lambda n: n.name):
+        if any(d < 0 for d in n.shape):
+            raise ValueError(f"{n.name}: a size that only a stored tensor gives; the "
+                             "configuration of a random model must name it")
         if device == "cpu":
             t = torch.randn(n.shape, generator=gen, dtype=torch.float32)
         else:
@@ -33,6 +38,11 @@ def random_tensors(needs: Iterable[TensorNeed], seed: int, std: float = 0.02,
             t = torch.empty(n.shape, dtype=dtype, device=device).normal_(0.0, 1.0, generator=gen)
         if n.role == "vector":
             t = t.mul_(norm_std).add_(1.0)
+        elif n.role == "fraction":
+            t = t.mul_(0.7071).erf_().add_(1.0).mul_(0.5)      # a normal draw made uniform
+        elif n.role == "identity":
+            t = t.mul_(norm_std).add_(torch.eye(n.shape[0], n.shape[1], dtype=t.dtype,
+                                                device=t.device))
         else:
             t = t.mul_(std)
         out[n.name] = t.to(dtype)
