@@ -180,18 +180,51 @@ def route(h, W, mlp: Dict, pre: str):
     z = z - z.max(axis=-1, keepdims=True)
     s = np.exp(z) / np.exp(z).sum(axis=-1, keepdims=True)
     choice = s + W[pre + "correction"]
+    if int(r.get("identity") or 0) + int(r["experts"]) != choice.shape[1]:
+        raise ValueError("the router's outputs are not experts + identity")
     order = np.argsort(-choice, axis=-1, kind="stable")
     ids = order[:, :top]
-    w = np.take_along_axis(s, ids, axis=-1) * float(r["scale"])
+    w = np.take_along_axis(s, ids, axis=-1) * float(r.get("scale", 1.0))
     ranked = np.take_along_axis(choice, order, axis=-1)
     margin = (ranked[:, top - 1] - ranked[:, top]) if choice.shape[1] > top else \
         np.full(h.shape[0], np.inf)
     return ids, w, margin
 
 
+class Routing:
+    """What a test wants to know of the routers' choices, or to settle about them.
+
+    ``margins[(layer, t)]``: how far the last chosen choice score of token t in layer ``layer``
+    lies above the first one left out, in units of the root mean square of the token's
+    scores. ``forced[(layer, t)]``: the experts that another implementation chose there; they
+    replace the plain choice where the two differ and the margin is below ``close`` (a
+    computation in 16 bits may fall on either side of such a call); where the margin is larger
+    the difference is an error."""
+
+    def __init__(self, forced=None, close: float = 0.08):
+        self.forced = forced or {}
+        self.close = close
+        self.margins: Dict = {}
+        self.replaced: List = []
+
+    def choose(self, layer, ids, w, margin, weights):
+        ids, w = ids.copy(), w.copy()
+        for t in range(ids.shape[0]):
+            self.margins[(layer, t)] = float(margin[t])
+            theirs = self.forced.get((layer, t))
+            if theirs is not None and set(int(e) for e in theirs) != set(ids[t].tolist()):
+                if margin[t] >= self.close:
+                    raise AssertionError(
+                        f"layer {layer}, token {t}: experts {sorted(theirs)} were chosen, "
+                        f"{sorted(ids[t].tolist())} expected, at a margin of {margin[t]:.3g}")
+                ids[t] = [int(e) for e in theirs]
+                w[t] = weights[t, ids[t]]
+                self.replaced.append((layer, t))
+        return ids, w
+
+
 def routed_feed_forward(h, W, mlp: Dict, pre: str, routing=None, tag=None) -> np.ndarray:
-    """``routing``: None, or an object with ``choose(tag, ids, w, margin, scores) -> ids, w``
-    that may settle close calls otherwise."""
+    """``routing``: None or a ``Routing``, which may settle close calls otherwise."""
     r = mlp["router"]
     real = int(r["experts"])
     ids, w, margin = route(h, W, mlp, pre)
@@ -199,7 +232,8 @@ def routed_feed_forward(h, W, mlp: Dict, pre: str, routing=None, tag=None) -> np
         z = h @ W[pre + "router"].T
         z = z - z.max(axis=-1, keepdims=True)
         s = np.exp(z) / np.exp(z).sum(axis=-1, keepdims=True)
-        ids, w = routing.choose(tag, ids, w, margin, s * float(r["scale"]))
+        rms = np.sqrt(np.mean(s * s, axis=-1))
+        ids, w = routing.choose(tag, ids, w, margin / rms, s * float(r.get("scale", 1.0)))
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
         for e, we in zip(ids[t], w[t]):

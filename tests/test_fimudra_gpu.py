@@ -1,0 +1,638 @@
+"""The Fimudra family on a B200 against the plain implementation, in float32 and bfloat16:
+each mechanism alone (with weights or inputs made so that a fault shows), then the engine on
+three small models of other sizes: whole prompts with the residual after every layer, prompts
+against token-by-token decoding, portions down to two tokens, unequal batches against each
+request alone, slots, pages and state used again, the first tokens, long decoding across page
+borders, decode graphs, and greedy generation through the entry point."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from mormot2_ai_b200 import Engine, Entry, LlmClient, PartSpec, Runtime
+from mormot2_ai_b200 import kernels as K
+from mormot2_ai_b200.cache.pages import PAGE, pages_for
+from mormot2_ai_b200.cache.storage import CacheLine
+from mormot2_ai_b200.parts import FEED_FORWARDS, MIXERS, POSITIONS
+from mormot2_ai_b200.parts.block import settle
+from mormot2_ai_b200.weights import random_tensors
+from tests.fimudra_models import SMALL, SmallModel
+from tests.gpu_helpers import DEV, make_step
+from tests.plain import fimudra_plain as plain
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+@pytest.fixture(scope="module", params=sorted(SMALL))
+def small(request, tmp_path_factory):
+    return SmallModel(request.param, str(tmp_path_factory.mktemp("fimudra_" + request.param)))
+
+
+@pytest.fixture(scope="module")
+def small_u(tmp_path_factory):
+    return SmallModel("U", str(tmp_path_factory.mktemp("fimudra_U_only")))
+
+
+class Choices:
+    """The experts that an engine's routers chose, by slot, layer and position, read through
+    the routed feed-forward's probe. In 16 bits a router may fall on the other side of a close
+    call than the plain implementation; the plain one then takes the engine's choice THERE
+    (``plain.Routing``), and a different choice anywhere else fails the test."""
+
+    def __init__(self, eng):
+        from mormot2_ai_b200.parts.moe import RoutedExperts
+        layers = eng.model.layers
+        self.runs = [i for i, r in enumerate(eng.model.spec.schedule)
+                     if isinstance(layers[r.layer].feed_forward, RoutedExperts)]
+        self.calls = 0
+        self.by_slot = {}
+        for layer in layers:
+            if isinstance(layer.feed_forward, RoutedExperts):
+                layer.feed_forward.probe = self.seen
+        eng.use_graphs = False
+
+    def seen(self, part, step, ids):
+        run = self.runs[self.calls % len(self.runs)]      # routers run in the order of the layers
+        self.calls += 1
+        rows = ids.cpu().numpy()
+        at = 0
+        for slot, past, new in zip(step.host_slots, step.host_past, step.host_new):
+            kept = self.by_slot.setdefault(slot, {})
+            for j in range(new):
+                kept[(run, past + j)] = rows[at + j].tolist()
+            at += new
+
+    def routing(self, slot):
+        return plain.Routing(forced=self.by_slot.pop(slot, {}))
+
+
+def engine_of(model, dtype, **kw):
+    kw.setdefault("max_tokens", 2048)
+    eng = Engine.from_folder(model.folder, dtype=dtype, **kw)
+    eng.choices = Choices(eng) if dtype == "bfloat16" else None
+    return eng
+
+
+def expected(model, eng, slot, ids, states=None):
+    routing = eng.choices.routing(slot) if eng.choices is not None else None
+    return model.reference(ids, states, routing)
+
+
+# The bounds of this family's comparisons, set from what was measured and never widened to
+# pass. float32: the largest difference of a logit over the largest logit; the recurrences
+# and the exponentials of the gates carry float32 rounding further than a feed-forward stack
+# does. bfloat16: per position, the largest difference of a logit over the spread of the
+# plain logits; every activation between kernels is rounded to 8 bits, and in these small
+# models single positions lie where that rounding is carried far (an output near zero before a
+# unit norm, gates at their cap), so the bound is on the median, the ninth decile and the
+# worst position of a comparison. A wrong key, state, page or slot fails the float32 bound by
+# orders of magnitude; the bfloat16 runs are there for the kernels that only they reach.
+F32_TOL = 5e-5
+BF16_TOL = {"median": 0.06, "decile": 0.15, "worst": 0.4}
+
+
+def check(got, want, dtype, what, wild=False):
+    """``wild``: the comparison is of model V in bfloat16, whose heads of five to ten values
+    carry the rounding far at single positions (a plain implementation that only rounds the
+    norms' outputs to 16 bits already differs there by a third of the spread): median and
+    ninth decile are bounded, the worst position is not."""
+    got, want = np.asarray(got, dtype=np.float64), np.asarray(want, dtype=np.float64)
+    assert got.shape == want.shape, (got.shape, want.shape)
+    record = os.environ.get("MORMOT_TOL_RECORD")
+    if dtype == "float32":
+        err = np.abs(got - want).max() / max(1.0, np.abs(want).max())
+        if record:
+            with open(record, "a") as f:
+                f.write(f"float32\t{err:.3e}\t{what}\n")
+        assert err <= F32_TOL, f"{what}: relative error {err:.3g} (float32)"
+        return
+    rows = np.abs(got - want).reshape(-1, want.shape[-1]).max(axis=1) / want.std()
+    med, dec, worst = np.median(rows), np.quantile(rows, 0.9), rows.max()
+    if record:
+        with open(record, "a") as f:
+            f.write(f"bfloat16\t{med:.3f}\t{dec:.3f}\t{worst:.3f}\t{len(rows)}\t{what}\n")
+    assert wild or worst <= BF16_TOL["worst"], \
+        f"{what}: a position off by {worst:.3g} of the spread"
+    if len(rows) >= 8:
+        assert med <= BF16_TOL["median"] and dec <= BF16_TOL["decile"], \
+            f"{what}: median {med:.3g}, ninth decile {dec:.3g} of the spread (bfloat16)"
+
+
+def part_weights(part, dtype, seed=0, std=0.1):
+    w = random_tensors(part.tensors(), seed, std=std, norm_std=0.2, dtype=torch.bfloat16)
+    return w, {k: v.double().numpy() for k, v in w.items()}
+
+
+def to_dev(w, dtype):
+    return {k: v.to(TORCH[dtype]).to(DEV) for k, v in w.items()}
+
+
+def rounded(a, dtype):
+    return torch.tensor(np.asarray(a), dtype=torch.float32).to(TORCH[dtype]).double().numpy()
+
+
+def line_of(n_slots, max_len, kv_heads, dim, vdim, dtype, seed=0):
+    """A cache line whose value rows have a size of their own, pages scrambled over the pool."""
+    per = pages_for(max_len)
+    n_pages = n_slots * per + 3
+    ids = np.random.default_rng(seed).permutation(n_pages)[:n_slots * per]
+    table = torch.tensor(ids.reshape(n_slots, per), dtype=torch.int32, device=DEV)
+    k = torch.zeros((n_pages, kv_heads, PAGE, dim), dtype=dtype, device=DEV)
+    v = torch.zeros((n_pages, kv_heads, PAGE, vdim), dtype=dtype, device=DEV)
+    return CacheLine(k, v, table, per, 0, 0, kv_heads, dim, 0 if vdim == dim else vdim)
+
+
+def run_mixer(mixer, hs, cuts, hidden, dtype, line=None, state=None):
+    """Feeds each sequence of ``hs`` (float arrays [n, hidden]) through the mixer in the
+    portions that ``cuts`` names (all sequences of a step together), from slots 2, 0, 1, ...;
+    returns the outputs per sequence."""
+    slots = [2, 0, 1, 3][:len(hs)]
+    outs = [[] for _ in hs]
+    for lo, hi in cuts:
+        seqs, rows = [], []
+        for b, h in enumerate(hs):
+            a, e = min(lo, len(h)), min(hi, len(h))
+            if e > a:
+                seqs.append((slots[b], a, [0] * (e - a), []))
+                rows.append((b, a, e))
+        if not seqs:
+            continue
+        step = make_step(seqs)
+        h = torch.tensor(np.concatenate([hs[b][a:e] for b, a, e in rows])).to(TORCH[dtype]).to(DEV)
+        x = torch.full((h.shape[0], hidden), 0.5, device=DEV)
+        pending = mixer.forward(h, x, step, line, state, True)
+        if pending is not None:                 # split sums that the next norm would add
+            settle(x, pending)
+        got = x.cpu().double().numpy() - 0.5
+        at = 0
+        for b, a, e in rows:
+            outs[b].append(got[at:at + e - a])
+            at += e - a
+    return [np.concatenate(o) for o in outs]
+
+
+# ---------------------------------------------------------------------------- mechanisms alone
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("S,H", [(1, 50), (3, 200), (8, 1031)])
+def test_streams_kernel(dtype, S, H):
+    """Write-back, read and layer norm in one pass; a row gather; the plain sum of streams."""
+    rng = np.random.default_rng(S)
+    T = 5
+    x = rng.normal(0, 2, (S, T, H)) + 3.0
+    mix, out, a = rng.normal(0, 1, (S, S)), rng.normal(0, 1, S), rng.normal(0, 1, S)
+    ys, fs = [rng.normal(0, 1, (T, H)) for _ in range(2)], [0.8, -0.5]
+    w = rounded(1 + 0.2 * rng.normal(0, 1, H), dtype)
+    f32 = lambda v: torch.tensor(v, dtype=torch.float32, device=DEV)
+    xd, h = f32(x), torch.empty((T, H), dtype=TORCH[dtype], device=DEV)
+    wd = f32(w).to(TORCH[dtype])
+    K.stream_step(xd, update=(f32(mix), f32(out), [(f32(y), f) for y, f in zip(ys, fs)]),
+                  read=(f32(a), wd, 1e-5, h, None, T))
+    y = fs[0] * ys[0] + fs[1] * ys[1]
+    new = np.stack([sum(mix[s, t] * x[s] for s in range(S)) + out[t] * y for t in range(S)])
+    assert np.allclose(xd.cpu().numpy(), new, rtol=1e-5, atol=1e-5)
+    u = sum(a[s] * new[s] for s in range(S))
+    check(h.float().cpu().numpy(), plain.layer_norm(u, w, 1e-5), dtype, "read after write-back")
+    rows = torch.tensor([4, 1], dtype=torch.int32, device=DEV)
+    g = torch.empty((2, H), dtype=TORCH[dtype], device=DEV)
+    K.stream_step(xd, read=(None, wd, 1e-5, g, rows, 2))
+    check(g.float().cpu().numpy(), plain.layer_norm(new.sum(0)[[4, 1]], w, 1e-5), dtype, "gather")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,dim,hidden", [(3, 12, 40), (2, 64, 96), (1, 33, 50)])
+def test_decaying_state_mixer_alone(dtype, heads, dim, hidden):
+    """Whole sequences, then the same in portions of 1, 2 and 30 tokens with a batch mate:
+    the state and the last row carry over; slots' states do not mix."""
+    rt = Runtime(TORCH[dtype])
+    p = {"heads": heads, "dim": dim}
+    names = {"mu_" + s: "mu." + s for s in "rkvgw"}
+    names.update({s: s for s in ("r", "k", "v", "g", "w1", "w2", "w0", "u", "norm", "o")})
+    mixer = MIXERS.build(PartSpec("wkv", {"hidden_size": hidden, "heads": heads, "dim": dim,
+                                          "eps": 1e-5, "decay_rank": 8, "names": names}), "m.")
+    w, ref = part_weights(mixer, dtype, seed=dim)
+    w["m.w0"] = w["m.w0"] - 2.0            # slow decays: tokens far back still count
+    ref["m.w0"] = w["m.w0"].double().numpy()
+    mixer.bind(to_dev(w, dtype), rt)
+    rng = np.random.default_rng(dim)
+    hs = [rounded(rng.normal(0, 1, (n, hidden)), dtype) for n in (70, 37)]
+    want = [plain.wkv_mixer(h, ref, p, "m.", 1e-5) for h in hs]
+    for cuts in ([(0, 70)], [(0, 1), (1, 3), (3, 33), (33, 34), (34, 70)]):
+        state = torch.zeros((4,) + mixer.state_need().shape, device=DEV)
+        state[1].fill_(7.0)                 # a slot that no sequence of the step uses
+        got = run_mixer(mixer, hs, cuts, hidden, dtype, state=state)
+        for g, wnt in zip(got, want):
+            check(g, wnt, dtype, f"cuts {cuts}")
+        assert bool((state[1] == 7.0).all())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,dim,vdim,hidden", [(3, 20, 12, 40), (2, 32, 64, 96), (1, 9, 22, 50)])
+def test_matrix_memory_mixer_alone(dtype, heads, dim, vdim, hidden):
+    rt = Runtime(TORCH[dtype])
+    p = {"heads": heads, "dim": dim, "vdim": vdim, "gate_cap": 6.0}
+    names = {s: s for s in ("q", "k", "v", "g", "o", "norm", "i", "f")}
+    names.update({"i_bias": "i.b", "f_bias": "f.b"})
+    mixer = MIXERS.build(PartSpec("mlstm", {"hidden_size": hidden, "heads": heads, "dim": dim,
+                                            "vdim": vdim, "gate_cap": 6.0, "eps": 1e-5,
+                                            "names": names}), "m.")
+    w, ref = part_weights(mixer, dtype, seed=vdim)
+    # gates that matter: large input gates now and then (the running maximum moves), a forget
+    # gate near 1 (far tokens still count) and the cap in reach
+    w["m.i"] = w["m.i"] * 20
+    w["m.f.b"] = w["m.f.b"] + 3.0
+    ref = {k: v.double().numpy() for k, v in w.items()}
+    mixer.bind(to_dev(w, dtype), rt)
+    rng = np.random.default_rng(vdim)
+    hs = [rounded(rng.normal(0, 1, (n, hidden)), dtype) for n in (66, 5)]
+    want = [plain.matrix_memory(h, ref, p, "m.", 1e-5) for h in hs]
+    for cuts in ([(0, 66)], [(0, 2), (2, 3), (3, 64), (64, 65), (65, 66)]):
+        state = torch.zeros((4,) + mixer.state_need().shape, device=DEV)
+        got = run_mixer(mixer, hs, cuts, hidden, dtype, state=state)
+        for g, wnt in zip(got, want):
+            check(g, wnt, dtype, f"cuts {cuts}")
+
+
+def attention_mixer(hidden, heads, kv, dim, vdim, rot, dtype, rt, seed=0):
+    positions = {}
+    if rot:
+        sc = rot.get("scaling") or {"factor": 1.0, "low": 1.0, "high": 1.0, "original": 1.0}
+        pos = POSITIONS.build(PartSpec("rope_scaled_bands", {
+            "theta": rot["base"], "rot_dim": rot["dims"], "factor": sc["factor"],
+            "low": sc["low"], "high": sc["high"], "original": sc["original"]}))
+        pos.bind({}, rt)
+        positions["r"] = pos
+    mixer = MIXERS.build(PartSpec("gqa_attention", {
+        "hidden_size": hidden, "heads": heads, "kv_heads": kv, "head_dim": dim, "v_dim": vdim,
+        "scale": 0.3, "position": "r" if rot else "",
+        "names": {"q": "q", "k": "k", "v": "v", "o": "o", "sink": "sink"}}), "a.",
+        positions=positions)
+    return mixer
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv,dim,vdim,rot", [
+    (4, 2, 24, 40, {"base": 1e4, "dims": 16, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0,
+                                                         "original": 64}}),
+    (3, 3, 10, 6, None),
+    (4, 1, 64, 64, {"base": 5e5, "dims": 64}),
+    (2, 1, 128, 128, {"base": 1e4, "dims": 64}),
+])
+def test_attention_with_a_sink_alone(dtype, heads, kv, dim, vdim, rot):
+    """Prompts over a page border and decoded tokens; a large sink in one head (its output
+    shrinks), a very negative one in another (as if there were none)."""
+    hidden = 72
+    rt = Runtime(TORCH[dtype])
+    mixer = attention_mixer(hidden, heads, kv, dim, vdim, rot, dtype, rt)
+    need = mixer.cache_need()
+    assert (need.head_dim, need.v_dim or need.head_dim) == (dim, vdim)
+    w, ref = part_weights(mixer, dtype, seed=dim)
+    w["a.sink"] = torch.tensor([4.0, -30.0, 0.5, 1.0][:heads], dtype=torch.bfloat16)
+    ref["a.sink"] = w["a.sink"].double().numpy()
+    mixer.bind(to_dev(w, dtype), rt)
+    p = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": 0.3, "rot": rot}
+    rng = np.random.default_rng(vdim)
+    hs = [rounded(rng.normal(0, 1, (n, hidden)), dtype) for n in (131, 9)]
+    want = [plain.sink_attention(h, ref, p, "a.", np.arange(len(h))) for h in hs]
+    line = line_of(3, 192, kv, dim, vdim, TORCH[dtype])
+    cuts = [(0, 3), (3, 65), (65, 128), (128, 129), (129, 130), (130, 131)]
+    got = run_mixer(mixer, hs, cuts, hidden, dtype, line=line)
+    for g, wnt in zip(got, want):
+        check(g, wnt, dtype, "portions and single tokens")
+    # the sink counts: without it the first token's output would be its own value row
+    no_sink = dict(ref, **{"a.sink": np.full(heads, -1e9)})
+    first = plain.sink_attention(hs[0][:1], no_sink, p, "a.", [0])
+    assert np.abs(first - want[0][:1]).max() > 1e-3
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("past", [63, 64, 700])
+def test_attention_finds_one_far_key_and_the_sink_beside_it(dtype, past):
+    """One key far back is made loud for the last query (the first key, one at a page border,
+    one in the middle); the output is then that key's value row, shrunk by the sink's share."""
+    heads, kv, dim, vdim = 2, 1, 32, 48
+    T = TORCH[dtype]
+    line = line_of(1, past + 1, kv, dim, vdim, T)
+    rng = np.random.default_rng(past)
+    keys = rounded(rng.normal(0, 0.1, (past + 1, dim)), dtype)
+    vals = rounded(rng.normal(0, 1, (past + 1, vdim)), dtype)
+    q = rounded(rng.normal(0, 1, (heads, dim)), dtype)
+    sink = np.array([2.0, -3.0])
+    table = line.page_table.cpu()
+    for loud in sorted({0, min(past, 64), past // 2}):
+        k = keys.copy()
+        k[loud] = rounded(q[0] * 40.0 / (q[0] @ q[0]), dtype)        # score 40 * scale for head 0
+        for pos in range(past + 1):
+            page = int(table[0, pos // PAGE])
+            line.k[page, 0, pos % PAGE] = torch.tensor(k[pos]).to(T).to(DEV)
+            line.v[page, 0, pos % PAGE] = torch.tensor(vals[pos]).to(T).to(DEV)
+        step = make_step([(0, past, [0], [])])
+        out = torch.empty((1, heads * vdim), dtype=T, device=DEV)
+        qd = torch.tensor(q.reshape(1, -1)).to(T).to(DEV)
+        K.attention_simt(qd, heads * dim, out, step, line, heads, kv, dim, 0, 0.5, vdim,
+                         torch.tensor(sink, dtype=torch.float32, device=DEV))
+        for h in range(heads):
+            s = (k @ q[h]) * 0.5
+            m = max(s.max(), sink[h])
+            e = np.exp(s - m)
+            want = (e @ vals) / (e.sum() + np.exp(sink[h] - m))
+            check(out.float().cpu().numpy()[0, h * vdim:(h + 1) * vdim], want, dtype,
+                  f"head {h}, loud key {loud} of {past + 1}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mixers_side_by_side_alone(dtype):
+    hidden = 64
+    rt = Runtime(TORCH[dtype])
+    rot = {"base": 1e4, "dims": 8}
+    pos = POSITIONS.build(PartSpec("rope_scaled_bands", {"theta": 1e4, "rot_dim": 8, "factor": 1.0,
+                                                         "low": 1.0, "high": 1.0, "original": 1.0}))
+    pos.bind({}, rt)
+    left = PartSpec("gqa_attention", {
+        "hidden_size": hidden, "heads": 2, "kv_heads": 1, "head_dim": 16, "v_dim": 24,
+        "scale": 0.25, "position": "r",
+        "names": {"q": "left.q", "k": "left.k", "v": "left.v", "o": "left.o", "sink": "left.sink"}})
+    right = PartSpec("mlstm", {
+        "hidden_size": hidden, "heads": 2, "dim": 12, "vdim": 20, "gate_cap": 9.0, "eps": 1e-5,
+        "names": {"q": "right.q", "k": "right.k", "v": "right.v", "g": "right.g", "o": "right.o",
+                  "norm": "right.norm", "i": "right.i", "f": "right.f", "i_bias": "right.i.b",
+                  "f_bias": "right.f.b"}})
+    mixer = MIXERS.build(PartSpec("side_by_side", {"branches": [
+        {"mixer": left, "scale": 0.7}, {"mixer": right, "scale": -1.3}]}), "m.",
+        positions={"r": pos})
+    assert mixer.cache_need().v_dim == 24 and mixer.state_need().shape == (2 * (12 * 20 + 12 + 1),)
+    w, ref = part_weights(mixer, dtype, seed=3)
+    mixer.bind(to_dev(w, dtype), rt)
+    p = {"left": {"heads": 2, "kv_heads": 1, "dim": 16, "vdim": 24, "scale": 0.25, "rot": rot},
+         "right": {"heads": 2, "dim": 12, "vdim": 20, "gate_cap": 9.0},
+         "left_scale": 0.7, "right_scale": -1.3}
+    rng = np.random.default_rng(5)
+    hs = [rounded(rng.normal(0, 1, (n, hidden)), dtype) for n in (40, 70)]
+    want = [plain.parallel_mixer(h, ref, p, "m.", 1e-5, np.arange(len(h))) for h in hs]
+    line = line_of(3, 128, 1, 16, 24, TORCH[dtype])
+    state = torch.zeros((4,) + mixer.state_need().shape, device=DEV)
+    got = run_mixer(mixer, hs, [(0, 38), (38, 39), (39, 70)], hidden, dtype, line=line, state=state)
+    for g, wnt in zip(got, want):
+        check(g, wnt, dtype, "two mixers side by side")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,E,ident,top,shared,ff,H", [
+    (5, 6, 1, 3, 28, 36, 80), (70, 4, 0, 1, 0, 20, 50), (3, 16, 3, 4, 96, 32, 128),
+    (200, 5, 2, 2, 14, 10, 64),
+])
+def test_routed_experts_with_identity_experts_alone(dtype, T, E, ident, top, shared, ff, H):
+    rt = Runtime(TORCH[dtype])
+    part = FEED_FORWARDS.build(PartSpec("routed_experts", {
+        "hidden_size": H, "experts": E, "top": top, "identity": ident, "route_scale": 1.7,
+        "intermediate_size": ff, "limit": 0.4, "shared_size": shared, "shared_limit": 0.9,
+        "shared_gate": False, "activation": "clamped_swish", "weights": "softmax_of_all",
+        "names": {"router": "router", "correction": "correction", "expert": "e{}.",
+                  "shared": "shared.", "gate": "gate", "up": "up", "down": "down"}}), "f.")
+    w, ref = part_weights(part, dtype, seed=T, std=0.3)     # many products beyond the limits
+    w["f.correction"] = (w["f.correction"] * 0.5).to(torch.bfloat16)
+    if ident:
+        w["f.correction"][-1] = 1.0        # the last identity expert is chosen by every token
+    ref = {k: v.double().numpy() for k, v in w.items()}
+    part.bind(to_dev(w, dtype), rt)
+    mlp = {"expert": {"ff": ff, "limit": 0.4},
+           "router": {"experts": E, "identity": ident, "top": top, "scale": 1.7}}
+    if shared:
+        mlp["shared"] = {"ff": shared, "limit": 0.9}
+    rng = np.random.default_rng(T)
+    h = rounded(rng.normal(0, 1, (T, H)), dtype)
+    seen = {}
+    part.probe = lambda part, step, ids: seen.update(ids=ids.cpu().numpy())
+    x = torch.full((T, H), 2.0, device=DEV)
+    part.forward(torch.tensor(h).to(TORCH[dtype]).to(DEV), x, make_step([(0, 0, [0] * T, [])]))
+    forced = {(0, t): seen["ids"][t].tolist() for t in range(T)}
+    routing = plain.Routing(forced=forced if dtype == "bfloat16" else {})
+    want = plain.routed_feed_forward(h, ref, mlp, "f.", routing, 0)
+    check(x.cpu().numpy() - 2.0, want, dtype, "routed experts")
+    if ident:
+        assert (seen["ids"] >= E).any()                      # an identity expert was chosen
+
+
+def test_router_kernel_scores_ties_and_correction():
+    """Scores over all outputs; equal choice scores go to the lower index; the correction
+    moves the choice and not the weight; the weights are not renormalized."""
+    z = torch.tensor([[1.0, 1.0, 1.0, 1.0, -2.0], [0.0, 3.0, 0.0, 3.0, 1.0],
+                      [2.0, 0.0, 0.0, 0.0, 0.0]], device=DEV)
+    corr = torch.tensor([0.0, 0.0, 0.0, 0.0, 5.0], device=DEV)
+    ids = torch.empty((3, 2), dtype=torch.int32, device=DEV)
+    w = torch.empty((3, 2), dtype=torch.float32, device=DEV)
+    K.moe_route(z, 5, 2, 5, ids, w, None, K.ROUTE_SOFTMAX_OF_ALL, corr, 1.5)
+    s = torch.softmax(z.cpu().double(), dim=-1).numpy()
+    assert ids.cpu().tolist() == [[4, 0], [4, 1], [4, 0]]
+    for t, row in enumerate(ids.cpu().tolist()):
+        assert np.allclose(w.cpu().numpy()[t], 1.5 * s[t, row], rtol=1e-6)
+
+
+# ---------------------------------------------------------------------------- the engine
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_whole_prompts_and_states_after_every_layer(small, dtype):
+    eng = engine_of(small, dtype)
+    for n in small.prompt_lens:
+        ids = small.tokens(n, seed=n)
+        states = []
+        eng.on_state = lambda name, x: states.append((name, x.cpu().numpy().copy()))
+        slot = eng.open()
+        out = eng.step([Entry(slot, ids, list(range(n)))])
+        eng.on_state = None
+        eng.close(slot)
+        want_states = []
+        want = expected(small, eng, slot, ids, want_states)
+        check(out.cpu().numpy(), want, dtype, f"{small.name}: whole prompt of {n}",
+              small.name == "V")
+        runs = [x for name, x in states if name.startswith("run")]
+        assert len(runs) == len(want_states) == len(small.doc["layers"])
+        for i, (got, ref) in enumerate(zip(runs, want_states)):
+            err = np.abs(got - ref).max(axis=1) / max(1.0, np.abs(ref).max())
+            if dtype == "float32":
+                assert err.max() <= F32_TOL, (n, i, err.max())
+            else:
+                assert np.median(err) <= 0.02, (n, i, np.median(err))
+                assert small.name == "V" or err.max() <= 0.15, (n, i, err.max())
+    eng.rt.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prompt_against_token_by_token_decoding(small, dtype):
+    """The last tokens one by one through the cache and the state, across a page border, and
+    a sequence that is decoded from its second token on."""
+    eng = engine_of(small, dtype)
+    for n, head in ((75, 58), (12, 1), (140, 126)):
+        ids = small.tokens(n, seed=100 + n)
+        slot = eng.open()
+        got = [eng.step([Entry(slot, ids[:head], [head - 1])]).cpu().numpy()]
+        for t in range(head, n):
+            got.append(eng.step([Entry(slot, [ids[t]])]).cpu().numpy().copy())
+        assert eng.length(slot) == n
+        eng.close(slot)
+        ref = expected(small, eng, slot, ids)
+        check(np.concatenate(got), ref[head - 1:], dtype, f"{n} tokens after a prompt of {head}",
+              small.name == "V")
+    eng.rt.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("chunk", [2, 7, 64])
+def test_portions_of_prompts(small, dtype, chunk):
+    eng = engine_of(small, dtype, prefill_chunk=chunk)
+    n = 131
+    ids = small.tokens(n, seed=500 + chunk)
+    slot = eng.open()
+    want = [0, 1, 62, 63, 64, 65, n - 1]
+    out = eng.step([Entry(slot, ids, want)]).cpu().numpy()
+    eng.close(slot)
+    check(out, expected(small, eng, slot, ids)[want], dtype, f"{n} tokens in passes of {chunk}",
+          small.name == "V")
+    slot = eng.open()
+    got = [eng.step([Entry(slot, ids[a:b], list(range(b - a)))]).cpu().numpy()
+           for a, b in ((0, 3), (3, 5), (5, 66), (66, n))]
+    eng.close(slot)
+    check(np.concatenate(got), expected(small, eng, slot, ids), dtype,
+          "steps of 3, 2, 61 and 65 tokens", small.name == "V")
+    eng.rt.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_unequal_batches_against_each_alone_with_reuse(small, dtype):
+    """Batches of unequal requests, one after another in three slots and just enough pages:
+    every logit equals that of the request's own whole pass; slots, pages and the slots'
+    state are given back and used again (a state that was not set back would show)."""
+    lens = small.prompt_lens + [2, 65, 33]
+    decode = [small.decode_steps, 3, 1, small.decode_steps, 5, 2, 4][:len(lens)]
+    lens = lens[:len(decode)]
+    pages = max(sum(-(-(n + d) // 64) for n, d in list(zip(lens, decode))[b0:b0 + 3])
+                for b0 in range(0, len(lens), 3))
+    eng = engine_of(small, dtype, max_tokens=64 * pages, max_slots=3)
+    reqs = [small.tokens(n + d, seed=200 + i) for i, (n, d) in enumerate(zip(lens, decode))]
+    for b0 in range(0, len(reqs), 3):
+        idx = list(range(b0, min(b0 + 3, len(reqs))))
+        slots = {i: eng.open() for i in idx}
+        mine = dict(slots)
+        assert sorted(slots.values()) == list(range(len(idx)))
+        got = {i: {} for i in idx}
+        out = eng.step([Entry(slots[i], reqs[i][:lens[i]]) for i in idx]).cpu().numpy()
+        for row, i in enumerate(idx):
+            got[i][lens[i] - 1] = out[row:row + 1]
+        at = {i: lens[i] for i in idx}
+        live = list(idx)
+        while live:
+            live = [i for i in live if at[i] < len(reqs[i])]
+            for i in idx:
+                if i not in live and i in slots:
+                    eng.close(slots.pop(i))
+            if not live:
+                break
+            out = eng.step([Entry(slots[i], [reqs[i][at[i]]]) for i in live]).cpu().numpy()
+            for row, i in enumerate(live):
+                got[i][at[i]] = out[row:row + 1].copy()
+                at[i] += 1
+        for i in idx:
+            ref = expected(small, eng, mine[i], reqs[i])
+            at_t = sorted(got[i])
+            check(np.concatenate([got[i][t] for t in at_t]), ref[at_t], dtype, f"request {i}",
+                  small.name == "V")
+    assert all(eng.book.held_pages(g) == 0 for g in range(len(eng.plans)))
+    assert eng.book.slots.free == 3
+    assert eng.faults() == []
+    eng.rt.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_batch_mates_do_not_matter(small_u, dtype):
+    small = small_u
+    eng = Engine.from_folder(small.folder, dtype=dtype, max_tokens=2048)
+    a = small.tokens(70, seed=1)
+    others = [small.tokens(n, seed=2 + n) for n in (3, 129)]
+    s = eng.open()
+    alone = [eng.step([Entry(s, a[:66], [0, 64, 65])]).cpu().numpy()]
+    alone += [eng.step([Entry(s, [t])]).cpu().numpy().copy() for t in a[66:]]
+    eng.close(s)
+    slots = [eng.open() for _ in range(3)]
+    out = eng.step([Entry(slots[0], others[0], []), Entry(slots[1], a[:66], [0, 64, 65]),
+                    Entry(slots[2], others[1], [])]).cpu().numpy()
+    tol = 1e-5 if dtype == "float32" else 3e-2
+    scale = np.abs(alone[0]).max()
+    assert np.abs(out - alone[0]).max() <= tol * scale
+    for k, t in enumerate(a[66:]):
+        out = eng.step([Entry(slots[0], [5]), Entry(slots[1], [t]), Entry(slots[2], [7])])
+        assert np.abs(out.cpu().numpy()[1:2] - alone[1 + k]).max() <= tol * scale
+    eng.rt.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_from_the_first_token(small_u, dtype):
+    small = small_u
+    eng = engine_of(small, dtype, max_tokens=512)
+    n = 200
+    ids = small.tokens(n, seed=300)
+    slot = eng.open()
+    got = [eng.step([Entry(slot, [t])]).cpu().numpy().copy() for t in ids]
+    eng.close(slot)
+    check(np.concatenate(got), expected(small, eng, slot, ids), dtype, "200 tokens one by one")
+    eng.rt.check()
+
+
+def test_a_step_that_fails_leaves_the_state_as_it_found_it(small_u):
+    """A refused step changes nothing, and after it the sequence goes on as if it had not been."""
+    small = small_u
+    eng = Engine.from_folder(small.folder, dtype="float32", max_tokens=256)
+    ids = small.tokens(40, seed=9)
+    slot = eng.open()
+    eng.step([Entry(slot, ids[:30], [])])
+    with pytest.raises(Exception):
+        eng.step([Entry(slot, [small.doc["vocab"] + 5])])
+    out = eng.step([Entry(slot, ids[30:], list(range(10)))]).cpu().numpy()
+    check(out, small.reference(ids)[30:], "float32", "after a refused step")
+
+
+def test_decode_graphs_replay_what_was_computed(small_u):
+    small = small_u
+    ids = [small.tokens(40 + 3 * i, seed=600 + i) for i in range(2)]
+    for dtype in DTYPES:
+        outs = {}
+        for graphs in (True, False):
+            eng = Engine.from_folder(small.folder, dtype=dtype, max_tokens=1024)
+            assert eng.use_graphs
+            eng.use_graphs = graphs
+            slots = [eng.open() for _ in ids]
+            eng.step([Entry(s, r[:30], []) for s, r in zip(slots, ids)])
+            outs[graphs] = [eng.step([Entry(s, [r[t]]) for s, r in zip(slots, ids)]).cpu().numpy().copy()
+                            for t in range(30, 40)]
+            assert len(eng.graphs) == (1 if graphs else 0)
+            eng.rt.check()
+        for a, b in zip(outs[True], outs[False]):
+            assert np.array_equal(a, b)
+        if dtype == "float32":
+            for row, r in enumerate(ids):
+                ref = small.reference(r)
+                check(np.concatenate([o[row:row + 1] for o in outs[True]]), ref[30:40], dtype,
+                      f"row {row}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_greedy_generation_through_the_entry_point(small, dtype):
+    client = LlmClient(small.folder, dtype=dtype, max_batch=3, cache_tokens=1024)
+    prompts = [small.tokens(n, seed=800 + n) for n in (4, 70, 17, 1)]
+    steps = small.decode_steps
+    got = client.generate(prompts, max_tokens=steps, temperature=0.0, stop=[])
+    for p, tokens in zip(prompts, got):
+        assert len(tokens) == steps
+        ids = list(p)
+        for i, a in enumerate(tokens):
+            routing = plain.Routing()
+            logits = small.reference(ids, routing=routing)[-1]
+            if dtype == "bfloat16" and min(routing.margins.values(), default=1.0) < routing.close:
+                break          # a router's close call: 16 bits may take the other side from here on
+            order = np.argsort(-logits, kind="stable")
+            if a != int(order[0]):
+                margin = float(logits[order[0]] - logits[order[1]])
+                assert dtype == "bfloat16" and margin < 0.06 * logits.std(), (i, a, margin)
+                break
+            ids.append(a)
+    assert all(client.engine.book.held_pages(g) == 0 for g in range(len(client.engine.plans)))
