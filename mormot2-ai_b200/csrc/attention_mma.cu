@@ -123,7 +123,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    const int* __restrict__ tok_pos, int nh,
                    int nkv, int window, float scale_log2, float* __restrict__ part_o,
                    float* __restrict__ part_ml, bf16* __restrict__ out, int out_stride,
-                   int in_clusters, int* __restrict__ error) {
+                   int in_clusters, int* __restrict__ error, const float* __restrict__ sink) {
   constexpr int CH = HD / 32;  // 32-dim chunks of q·k
   constexpr int DB = HD / 64;  // 64-dim blocks of p·v
   constexpr uint32_t TILE = MB_PAGE * HD * 2;  // bytes of a page's keys (or values)
@@ -325,11 +325,14 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
   __syncthreads();
   for (int idx = threadIdx.x; idx < rows_valid * HD; idx += blockDim.x) {
     const int row = idx / HD, d = idx - row * HD;
-    float M = -INFINITY;
+    // a sink: one more term exp(sink[h]) in the denominator, counted once, by the first split
+    const float sk = (sink != nullptr && s == 0) ? sink[h0 + row] * 1.4426950408889634f : -INFINITY;
+    float M = sk;
 #pragma unroll
     for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, sm_m[w * 16 + row]);
     float L = 0.f, acc = 0.f;
     if (M > -INFINITY) {
+      if (sk > -INFINITY) L = exp2f(sk - M);
 #pragma unroll
       for (int w = 0; w < DEC_WARPS; ++w) {
         const float f = exp2f(sm_m[w * 16 + row] - M);  // 0 for a warp without keys
@@ -430,7 +433,7 @@ static int decode_launch(const void* q, int q_stride, void* out, int out_stride,
                          int max_pages, int ring_pages, const int* tok_slot, const int* tok_pos,
                          int T, int nh, int nkv, int hd, int window, float scale, int splits,
                          float* part_o, float* part_ml, int in_clusters, int* error,
-                         cudaStream_t s) {
+                         cudaStream_t s, const float* sink = nullptr) {
   const int G = nh / nkv, subs = (G + 15) / 16;
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(splits, nkv * subs, T), mgrid(T, nh);
@@ -449,12 +452,12 @@ static int decode_launch(const void* q, int q_stride, void* out, int out_stride,
                          splits, (const bf16*)q, q_stride, (const bf16*)kpool,                 \
                          (const bf16*)vpool, page_table, max_pages, ring_pages, tok_slot,      \
                          tok_pos, nh, nkv, window, scale_log2, part_o, part_ml, (bf16*)out,    \
-                         out_stride, 1, error);                                                \
+                         out_stride, 1, error, sink);                                          \
     } else {                                                                                   \
       mb_launch(attn_decode_kernel<HD_>, grid, dim3((DEC_WARPS + 1) * 32), smem, s,            \
                 (const bf16*)q, q_stride, (const bf16*)kpool, (const bf16*)vpool, page_table,  \
                 max_pages, ring_pages, tok_slot, tok_pos, nh, nkv, window, scale_log2, part_o, \
-                part_ml, (bf16*)out, out_stride, in_clusters, error);                          \
+                part_ml, (bf16*)out, out_stride, in_clusters, error, sink);                    \
       if (!in_clusters)                                                                        \
         mb_launch(attn_merge_kernel<HD_>, mgrid, dim3(HD_), 0, s, (const float*)part_o,        \
                   (const float*)part_ml, splits, (bf16*)out, out_stride, nh);                  \
@@ -477,7 +480,8 @@ MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int ou
                                   int max_pages, int ring_pages, const int* tok_slot,
                                   const int* tok_pos, int T, int nh, int nkv,
                                   int hd, int window, float scale, int splits, float* scratch,
-                                  long long scratch_floats, int* error, void* stream) {
+                                  long long scratch_floats, int* error, const float* sink,
+                                  void* stream) {
   if (T <= 0) return 0;
   if (decode_checks(q, q_stride, kpool, vpool, T, nh, nkv, hd, splits)) return -1;
   const long long need = mb_attention_decode_scratch(T, nh, hd, splits);
@@ -486,7 +490,7 @@ MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int ou
   return decode_launch(q, q_stride, out, out_stride, kpool, vpool, page_table, max_pages,
                        ring_pages, tok_slot, tok_pos, T, nh, nkv, hd, window, scale, splits,
                        scratch, scratch + (size_t)T * nh * splits * hd, 0, error,
-                       (cudaStream_t)stream);
+                       (cudaStream_t)stream, sink);
 }
 
 // The same with the splits of a (token, group of heads) as the CTAs of one thread-block
@@ -499,7 +503,8 @@ MB_EXPORT int mb_attention_decode_clusters(const void* q, int q_stride, void* ou
                                            const int* page_table, int max_pages, int ring_pages,
                                            const int* tok_slot, const int* tok_pos, int T,
                                            int nh, int nkv, int hd, int window, float scale,
-                                           int splits, int* error, void* stream) {
+                                           int splits, int* error, const float* sink,
+                                           void* stream) {
   if (T <= 0) return 0;
   if (decode_checks(q, q_stride, kpool, vpool, T, nh, nkv, hd, splits)) return -1;
   if (splits > MB_DECODE_CLUSTER_SPLITS)
@@ -508,7 +513,7 @@ MB_EXPORT int mb_attention_decode_clusters(const void* q, int q_stride, void* ou
   if (((uintptr_t)out & 1)) MB_FAIL("mb_attention_decode_clusters: out is not aligned");
   return decode_launch(q, q_stride, out, out_stride, kpool, vpool, page_table, max_pages,
                        ring_pages, tok_slot, tok_pos, T, nh, nkv, hd, window, scale, splits,
-                       nullptr, nullptr, 1, error, (cudaStream_t)stream);
+                       nullptr, nullptr, 1, error, (cudaStream_t)stream, sink);
 }
 
 // ------------------------------------------------------------------ prefill
@@ -586,7 +591,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
                     const bf16* __restrict__ vpool, const int* __restrict__ page_table,
                     int max_pages, int ring_pages, const int* __restrict__ seq_start,
                     const int* __restrict__ seq_past, const int* __restrict__ seq_slot, int nh,
-                    int nkv, int window, float scale_log2) {
+                    int nkv, int window, float scale_log2, const float* __restrict__ sink) {
   mb_grid_wait();
   mb_grid_launch_next();
   constexpr int CH = HD / 32, DB = HD / 64;
@@ -647,6 +652,13 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
     load_q<HD>(has_a ? qrow : nullptr, has_b ? qrow + (size_t)8 * q_stride : nullptr, c, qa, qb);
   }
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  if (sink != nullptr) {
+    // one more term exp(sink[h]) in every row's denominator: a key of that score whose value
+    // is zero; the row sums are added over the four lanes of a row at the end, so one lane
+    // counts it
+    m0 = m1 = sink[h] * 1.4426950408889634f;
+    l0 = l1 = c == 0 ? 1.f : 0.f;
+  }
   float o[DB][8][4];
 #pragma unroll
   for (int db = 0; db < DB; ++db)
@@ -752,7 +764,7 @@ MB_EXPORT int mb_attention_prefill(const void* q, int q_stride, void* out, int o
                                    int max_pages, int ring_pages, const int* seq_start,
                                    const int* seq_past, const int* seq_slot, int B, int max_new,
                                    int nh, int nkv, int hd, int window, float scale, int* error,
-                                   void* stream) {
+                                   const float* sink, void* stream) {
   if (B <= 0 || max_new <= 0) return 0;
   if (hd != 64 && hd != 128)
     MB_FAIL("mb_attention_prefill: heads of %d values are not supported (64 or 128)", hd);
@@ -777,7 +789,7 @@ MB_EXPORT int mb_attention_prefill(const void* q, int q_stride, void* out, int o
     mb_launch(attn_prefill_kernel<HD_>, grid, dim3(DEC_WARPS * 32), smem, s, (const bf16*)q,   \
               q_stride, (bf16*)out, out_stride, (const bf16*)kpool, (const bf16*)vpool,        \
               page_table, max_pages, ring_pages, seq_start, seq_past, seq_slot, nh, nkv,       \
-              window, scale_log2);                                                             \
+              window, scale_log2, sink);                                                       \
   }
   if (hd == 64) GO(64) else GO(128)
 #undef GO
@@ -828,5 +840,5 @@ MB_EXPORT int mb_attention_decode_static(const void* q, int q_stride, void* out,
   return mb_attention_decode(q, q_stride, out, out_stride, kpool, vpool, page_table, max_pages,
                              ring_pages, tok_slot, tok_pos, T, nh, nkv, hd, window,
                              scale, splits, g_static_scratch_ptr[device],
-                             MB_ATTENTION_DECODE_STATIC_FLOATS, error, stream);
+                             MB_ATTENTION_DECODE_STATIC_FLOATS, error, nullptr, stream);
 }

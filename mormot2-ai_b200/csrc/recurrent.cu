@@ -3,8 +3,8 @@
 // mixer's part of a slot's row starts at `state_off`), is read when a step begins and written
 // when it ends, so a sequence may be fed in portions of any size. Everything that enters a
 // recurrence is float32: decays, gates, maxima, norms. One block per (sequence, head) walks the
-// step's tokens of its sequence in order; a thread owns one value column of the head's matrix
-// state, which is kept in shared memory.
+// step's tokens of its sequence in order, sixteen at a time staged in shared memory; a thread
+// owns one value column of the head's matrix state, which is kept in shared memory.
 //
 //   token_shift   mix_s[t] = h[t] + (h[t-1] - h[t]) mu_s   for several s at once; h[-1] of a
 //                 sequence is kept in the state (zeros before the first token)
@@ -58,32 +58,12 @@ MB_EXPORT int mb_token_shift(const void* h, int dtype, const float* state, long 
   MB_CHECK_LAUNCH("mb_token_shift");
 }
 
-// Two sums over the block at once; `red` holds 66 floats.
-__device__ __forceinline__ float2 block_sum2(float a, float b, float* red) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  a = warp_sum(a);
-  b = warp_sum(b);
-  __syncthreads();
-  if (lane == 0) {
-    red[warp] = a;
-    red[33 + warp] = b;
-  }
-  __syncthreads();
-  if (warp == 0) {
-    const int nw = (blockDim.x + 31) >> 5;
-    float ta = lane < nw ? red[lane] : 0.f, tb = lane < nw ? red[33 + lane] : 0.f;
-    ta = warp_sum(ta);
-    tb = warp_sum(tb);
-    if (lane == 0) {
-      red[32] = ta;
-      red[65] = tb;
-    }
-  }
-  __syncthreads();
-  return make_float2(red[32], red[65]);
-}
-
 // ------------------------------------------------------------------ decaying matrix state
+// A block stages SCAN_CT tokens of its head's inputs in shared memory at once (all loads in
+// flight together), walks them without a barrier between tokens (a thread reads the staged
+// vectors and its own column of the state), and then norms the chunk's outputs a warp a token.
+#define SCAN_CT 16
+
 // r, k, v, lw, g: float32 [T, ld] each (head hd's values at column hd * D + i); w0, u, normw:
 // float32 [H * D]. State of a slot: [W values of the last h | H x D x D]. out [T, H * D].
 template <typename T>
@@ -98,54 +78,68 @@ __global__ void wkv_scan_kernel(const float* __restrict__ r, const float* __rest
                                 int D) {
   mb_grid_wait();
   mb_grid_launch_next();
-  extern __shared__ float wk_smem[];
-  float* S = wk_smem;            // [D][D], S[i * D + j]: key channel i, value channel j
-  float* sr = S + D * D;         // [D] r
-  float* sk = sr + D;            // [D] k
-  float* sw = sk + D;            // [D] decay
-  float* su = sw + D;            // [D] u * k
-  float* red = su + D;           // 33
+  extern __shared__ __align__(16) float wk_smem[];
+  const int DD = (D * D + 3) & ~3;
+  float* S = wk_smem;                        // [D][D], S[i * D + j]: key channel i, value channel j
+  float4* vec = (float4*)(S + DD);           // [CT][D]: r, k, decay, u * k
+  float* sv = (float*)(vec + SCAN_CT * D);   // [CT][D] v
+  float* sg = sv + SCAN_CT * D;              // [CT][D] g
+  float* so = sg + SCAN_CT * D;              // [CT][D] o
   const int b = blockIdx.x, hd = blockIdx.y, j = threadIdx.x;
+  const int warp = j >> 5, lane = j & 31, warps = blockDim.x >> 5;
   const int t0 = seq_start[b], n = seq_start[b + 1] - t0;
   float* st = state + (size_t)seq_slot[b] * state_stride + state_off;
   float* Sg = st + W + (size_t)hd * D * D;
   for (int e = j; e < D * D; e += blockDim.x) S[e] = Sg[e];
   const bool own = j < D;
   const int col = hd * D + j;
-  const float w0j = own ? w0[col] : 0.f, uj = own ? u[col] : 0.f, nwj = own ? normw[col] : 0.f;
-  __syncthreads();
-  for (int t = t0; t < t0 + n; ++t) {
-    const size_t at = (size_t)t * ld + col;
-    float vj = 0.f, gj = 0.f;
+  const float w0j = own ? w0[col] : 0.f, uj = own ? u[col] : 0.f;
+  for (int c0 = 0; c0 < n; c0 += SCAN_CT) {
+    const int cn = min(SCAN_CT, n - c0);
     if (own) {
-      const float kj = k[at];
-      sr[j] = r[at];
-      sk[j] = kj;
-      sw[j] = expf(-expf(lw[at] + w0j));
-      su[j] = uj * kj;
-      vj = v[at];
-      gj = g[at];
-    }
-    __syncthreads();
-    float o = 0.f;
-    if (own) {
-      for (int i = 0; i < D; ++i) {
-        const float s = S[i * D + j];
-        o = fmaf(sr[i], fmaf(su[i], vj, s), o);
-        S[i * D + j] = fmaf(sw[i], s, sk[i] * vj);
+      for (int tt = 0; tt < cn; ++tt) {
+        const size_t at = (size_t)(t0 + c0 + tt) * ld + col;
+        const float kj = k[at];
+        vec[tt * D + j] = make_float4(r[at], kj, expf(-expf(lw[at] + w0j)), uj * kj);
+        sv[tt * D + j] = v[at];
+        sg[tt * D + j] = g[at];
       }
     }
-    const float ss = block_sum(own ? o * o : 0.f, red);   // also keeps the vectors' readers apart
+    __syncthreads();
     if (own) {
-      const float inv = 1.0f / sqrtf(ss / (float)D + eps);
-      const float gate = gj / (1.0f + expf(-gj));
-      out[(size_t)t * H * D + col] = from_f32<T>(o * inv * nwj * gate);
+      for (int tt = 0; tt < cn; ++tt) {
+        const float vj = sv[tt * D + j];
+        const float4* x = vec + tt * D;
+        float o = 0.f;
+        for (int i = 0; i < D; ++i) {
+          const float4 xi = x[i];
+          const float s = S[i * D + j];
+          o = fmaf(xi.x, fmaf(xi.w, vj, s), o);
+          S[i * D + j] = fmaf(xi.z, s, xi.y * vj);
+        }
+        so[tt * D + j] = o;
+      }
     }
+    __syncthreads();
+    for (int tt = warp; tt < cn; tt += warps) {
+      float ss = 0.f;
+      for (int i = lane; i < D; i += 32) ss = fmaf(so[tt * D + i], so[tt * D + i], ss);
+      const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
+      T* orow = out + (size_t)(t0 + c0 + tt) * H * D + hd * D;
+      for (int i = lane; i < D; i += 32) {
+        const float gi = sg[tt * D + i];
+        orow[i] = from_f32<T>(so[tt * D + i] * inv * normw[hd * D + i] * (gi / (1.0f + expf(-gi))));
+      }
+    }
+    __syncthreads();
   }
-  __syncthreads();
   for (int e = j; e < D * D; e += blockDim.x) Sg[e] = S[e];
   if (hd == 0 && n > 0)
     for (int c = j; c < W; c += blockDim.x) st[c] = to_f32<T>(h[(size_t)(t0 + n - 1) * W + c]);
+}
+
+static size_t wkv_smem_bytes(int D) {
+  return ((size_t)((D * D + 3) & ~3) + (size_t)SCAN_CT * D * 7) * sizeof(float);
 }
 
 MB_EXPORT int mb_wkv_scan(const float* r, const float* k, const float* v, const float* lw,
@@ -155,7 +149,7 @@ MB_EXPORT int mb_wkv_scan(const float* r, const float* k, const float* v, const 
                           const int* seq_start, const int* seq_slot, void* out, int B, int H,
                           int D, void* stream) {
   if (B <= 0) return 0;
-  const size_t smem = ((size_t)D * D + 4 * D + 33) * sizeof(float);
+  const size_t smem = wkv_smem_bytes(D);
   if (D <= 0 || D > 1024 || smem > 200 * 1024)
     MB_FAIL("mb_wkv_scan: heads of %d values (the state of a head must fit 200 KB)", D);
   cudaStream_t s = (cudaStream_t)stream;
@@ -197,65 +191,93 @@ __global__ void mlstm_scan_kernel(const float* __restrict__ z, int ld, int cq, i
                                   int D, int DV) {
   mb_grid_wait();
   mb_grid_launch_next();
-  extern __shared__ float ml_smem[];
-  float* S = ml_smem;          // [D][DV]
-  float* sq = S + D * DV;      // [D]
-  float* sk = sq + D;          // [D]
-  float* sc = sk + D;          // a, b, exp(-m')
-  float* red = sc + 4;         // 66
+  extern __shared__ __align__(16) float ml_smem[];
+  const int DD = (D * DV + 3) & ~3;
+  float* S = ml_smem;                          // [D][DV]
+  float2* qk = (float2*)(S + DD);              // [CT][D]: q (scaled), k
+  float* sv = (float*)(qk + SCAN_CT * D);      // [CT][DV] v
+  float* sg = sv + SCAN_CT * DV;               // [CT][DV] the output gate's logit
+  float* snum = sg + SCAN_CT * DV;             // [CT][DV] S^T q
+  float* snq = snum + SCAN_CT * DV;            // [CT][D] n_i q_i
+  float* sab = snq + SCAN_CT * D;              // [CT][4]: the state's factor, the input's, e^(-m)
   const int b = blockIdx.x, hd = blockIdx.y, j = threadIdx.x;
+  const int warp = j >> 5, lane = j & 31, warps = blockDim.x >> 5;
   const int t0 = seq_start[b], n = seq_start[b + 1] - t0;
   float* st = state + (size_t)seq_slot[b] * state_stride + state_off +
               (size_t)hd * ((size_t)D * DV + D + 1);
   for (int e = j; e < D * DV; e += blockDim.x) S[e] = st[e];
   const bool own_k = j < D, own_v = j < DV;
   float nj = own_k ? st[(size_t)D * DV + j] : 0.f;
-  float m = st[(size_t)D * DV + D];
+  float m = st[(size_t)D * DV + D];          // thread 0's copy is the one that counts
   const float bih = bi[hd], bfh = bf[hd];
-  const float nwj = own_v ? normw[hd * DV + j] : 0.f;
-  __syncthreads();
-  for (int t = t0; t < t0 + n; ++t) {
-    const float* zr = z + (size_t)t * ld;
-    // every thread forms the gates itself (two values, the same arithmetic in each)
-    const float gi = cap * tanhf((zr[ci + hd] + bih) / cap);
-    const float gf = log_sigmoid(cap * tanhf((zr[cf + hd] + bfh) / cap));
-    const float m_new = fmaxf(gf + m, gi);
-    const float a = expf(gf + m - m_new), bb = expf(gi - m_new);
-    m = m_new;
-    float qj = 0.f, kj = 0.f, vj = 0.f, gj = 0.f;
-    if (own_k) {
-      qj = zr[cq + hd * D + j] * q_scale;
-      kj = zr[ck + hd * D + j];
-      sq[j] = qj;
-      sk[j] = kj;
-      nj = fmaf(a, nj, bb * kj);
-    }
-    if (own_v) {
-      vj = zr[cv + hd * DV + j];
-      gj = zr[cg + hd * DV + j];
-    }
-    __syncthreads();
-    float num = 0.f;
-    if (own_v) {
-      const float bv = bb * vj;
-      for (int i = 0; i < D; ++i) {
-        const float s = fmaf(a, S[i * DV + j], sk[i] * bv);
-        S[i * DV + j] = s;
-        num = fmaf(s, sq[i], num);
+  for (int c0 = 0; c0 < n; c0 += SCAN_CT) {
+    const int cn = min(SCAN_CT, n - c0);
+    for (int tt = 0; tt < cn; ++tt) {
+      const float* zr = z + (size_t)(t0 + c0 + tt) * ld;
+      if (own_k) qk[tt * D + j] = make_float2(zr[cq + hd * D + j] * q_scale, zr[ck + hd * D + j]);
+      if (own_v) {
+        sv[tt * DV + j] = zr[cv + hd * DV + j];
+        sg[tt * DV + j] = zr[cg + hd * DV + j];
       }
     }
-    const float2 sums = block_sum2(own_k ? nj * qj : 0.f, own_v ? num * num : 0.f, red);
-    if (own_v) {
-      const float den = fmaxf(fabsf(sums.x), expf(-m)) + 1e-6f;
-      const float inv = 1.0f / sqrtf(sums.y / (den * den) / (float)DV + eps);
-      const float gate = 1.0f / (1.0f + expf(-gj));
-      out[(size_t)t * H * DV + hd * DV + j] = from_f32<T>(num / den * inv * nwj * gate);
+    if (j == 0) {
+      // the gates and the running maximum, token after token
+      for (int tt = 0; tt < cn; ++tt) {
+        const float* zr = z + (size_t)(t0 + c0 + tt) * ld;
+        const float gi = cap * tanhf((zr[ci + hd] + bih) / cap);
+        const float gf = log_sigmoid(cap * tanhf((zr[cf + hd] + bfh) / cap));
+        const float m_new = fmaxf(gf + m, gi);
+        sab[tt * 4] = expf(gf + m - m_new);
+        sab[tt * 4 + 1] = expf(gi - m_new);
+        sab[tt * 4 + 2] = expf(-m_new);
+        m = m_new;
+      }
     }
+    __syncthreads();
+    for (int tt = 0; tt < cn; ++tt) {
+      const float a = sab[tt * 4], bb = sab[tt * 4 + 1];
+      if (own_k) {
+        const float2 x = qk[tt * D + j];
+        nj = fmaf(a, nj, bb * x.y);
+        snq[tt * D + j] = nj * x.x;
+      }
+      if (own_v) {
+        const float bv = bb * sv[tt * DV + j];
+        const float2* x = qk + tt * D;
+        float num = 0.f;
+        for (int i = 0; i < D; ++i) {
+          const float2 xi = x[i];
+          const float s = fmaf(a, S[i * DV + j], xi.y * bv);
+          S[i * DV + j] = s;
+          num = fmaf(s, xi.x, num);
+        }
+        snum[tt * DV + j] = num;
+      }
+    }
+    __syncthreads();
+    for (int tt = warp; tt < cn; tt += warps) {
+      float nq = 0.f, ss = 0.f;
+      for (int i = lane; i < D; i += 32) nq += snq[tt * D + i];
+      for (int i = lane; i < DV; i += 32) ss = fmaf(snum[tt * DV + i], snum[tt * DV + i], ss);
+      nq = warp_sum(nq);
+      ss = warp_sum(ss);
+      const float den = fmaxf(fabsf(nq), sab[tt * 4 + 2]) + 1e-6f;
+      const float inv = 1.0f / sqrtf(ss / (den * den) / (float)DV + eps);
+      T* orow = out + (size_t)(t0 + c0 + tt) * H * DV + hd * DV;
+      for (int i = lane; i < DV; i += 32) {
+        const float gate = 1.0f / (1.0f + expf(-sg[tt * DV + i]));
+        orow[i] = from_f32<T>(snum[tt * DV + i] / den * inv * normw[hd * DV + i] * gate);
+      }
+    }
+    __syncthreads();
   }
-  __syncthreads();
   for (int e = j; e < D * DV; e += blockDim.x) st[e] = S[e];
   if (own_k) st[(size_t)D * DV + j] = nj;
   if (j == 0) st[(size_t)D * DV + D] = m;
+}
+
+static size_t mlstm_smem_bytes(int D, int DV) {
+  return ((size_t)((D * DV + 3) & ~3) + (size_t)SCAN_CT * (3 * D + 3 * DV + 4)) * sizeof(float);
 }
 
 MB_EXPORT int mb_mlstm_scan(const float* z, int ld, int cq, int ck, int cv, int cg, int ci, int cf,
@@ -264,7 +286,7 @@ MB_EXPORT int mb_mlstm_scan(const float* z, int ld, int cq, int ck, int cv, int 
                             long long state_off, const int* seq_start, const int* seq_slot,
                             void* out, int dtype, int B, int H, int D, int DV, void* stream) {
   if (B <= 0) return 0;
-  const size_t smem = ((size_t)D * DV + 2 * D + 4 + 66) * sizeof(float);
+  const size_t smem = mlstm_smem_bytes(D, DV);
   if (D <= 0 || DV <= 0 || D > 1024 || DV > 1024 || smem > 200 * 1024)
     MB_FAIL("mb_mlstm_scan: heads of %d x %d values (the state of a head must fit 200 KB)", D, DV);
   cudaStream_t s = (cudaStream_t)stream;

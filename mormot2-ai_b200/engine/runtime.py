@@ -161,8 +161,9 @@ class Runtime:
                   sink=None) -> None:
         """``vd``: the size of a value row where it differs from ``hd``; ``sink``: float32
         [nh], one more term of every softmax denominator."""
-        if self.fast_kernels and (not vd or vd == hd) and sink is None:
+        if self.fast_kernels and (not vd or vd == hd):
             from ..parts import attention_fast
-            if attention_fast.run(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale):
+            if attention_fast.run(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale,
+                                  sink):
                 return
         K.attention_simt(q, q_stride, out, step, line, nh, nkv, hd, window, scale, vd, sink)

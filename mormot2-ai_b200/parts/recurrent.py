@@ -47,7 +47,7 @@ class WkvMixer(Part):
         self.rank = int(p.get("decay_rank") or -1)
         self.names = {k: prefix + v for k, v in p["names"].items()}
         self.width = self.nh * self.dim
-        if (self.dim * self.dim + 4 * self.dim + 33) * 4 > 200 * 1024:
+        if (self.dim * self.dim + 4 + 7 * 16 * self.dim) * 4 > 200 * 1024:
             raise ConfigError(f"a decaying state of {self.dim} x {self.dim} values per head is "
                               "more than the kernel keeps in shared memory")
 
@@ -110,7 +110,7 @@ class MlstmMixer(Part):
         if self.cap <= 0:
             raise ConfigError(f"a gate cap of {self.cap}")
         self.names = {k: prefix + v for k, v in p["names"].items()}
-        if (self.dim * self.vdim + 2 * self.dim + 70) * 4 > 200 * 1024:
+        if (self.dim * self.vdim + 4 + 16 * (3 * self.dim + 3 * self.vdim + 4)) * 4 > 200 * 1024:
             raise ConfigError(f"a matrix memory of {self.dim} x {self.vdim} values per head is "
                               "more than the kernel keeps in shared memory")
 

@@ -309,10 +309,14 @@ def test_attention_with_a_sink_alone(dtype, heads, kv, dim, vdim, rot):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("past", [63, 64, 700])
-def test_attention_finds_one_far_key_and_the_sink_beside_it(dtype, past):
+@pytest.mark.parametrize("dim,vdim", [(32, 48), (64, 64), (128, 128)])
+def test_attention_finds_one_far_key_and_the_sink_beside_it(dtype, past, dim, vdim):
     """One key far back is made loud for the last query (the first key, one at a page border,
-    one in the middle); the output is then that key's value row, shrunk by the sink's share."""
-    heads, kv, dim, vdim = 2, 1, 32, 48
+    one in the middle); the output is then that key's value row, shrunk by the sink's share.
+    Heads of 64 and 128 values go to the tensor-core kernels in bfloat16 (a decode step's keys
+    dealt out over several blocks, of which one counts the sink), the others to the general one."""
+    heads, kv = 2, 1
+    rt = Runtime(TORCH[dtype])
     T = TORCH[dtype]
     line = line_of(1, past + 1, kv, dim, vdim, T)
     rng = np.random.default_rng(past)
@@ -323,7 +327,7 @@ def test_attention_finds_one_far_key_and_the_sink_beside_it(dtype, past):
     table = line.page_table.cpu()
     for loud in sorted({0, min(past, 64), past // 2}):
         k = keys.copy()
-        k[loud] = rounded(q[0] * 40.0 / (q[0] @ q[0]), dtype)        # score 40 * scale for head 0
+        k[loud] = rounded(q[0] * 24.0 / (q[0] @ q[0]), dtype)        # score 24 * scale for head 0
         for pos in range(past + 1):
             page = int(table[0, pos // PAGE])
             line.k[page, 0, pos % PAGE] = torch.tensor(k[pos]).to(T).to(DEV)
@@ -331,8 +335,8 @@ def test_attention_finds_one_far_key_and_the_sink_beside_it(dtype, past):
         step = make_step([(0, past, [0], [])])
         out = torch.empty((1, heads * vdim), dtype=T, device=DEV)
         qd = torch.tensor(q.reshape(1, -1)).to(T).to(DEV)
-        K.attention_simt(qd, heads * dim, out, step, line, heads, kv, dim, 0, 0.5, vdim,
-                         torch.tensor(sink, dtype=torch.float32, device=DEV))
+        rt.attention(qd, heads * dim, out, step, line, heads, kv, dim, 0, 0.5, vd=vdim,
+                     sink=torch.tensor(sink, dtype=torch.float32, device=DEV))
         for h in range(heads):
             s = (k @ q[h]) * 0.5
             m = max(s.max(), sink[h])
