@@ -1,7 +1,7 @@
 """Measures decoding and prefill of the Qwen3-8B shape with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --design busavik [--sizes small,mid]     (another workload, see below)
+    python bench.py --design busavik|fimudra [--sizes small,mid]   (another workload, see below)
 
 A step is one decode step of a batch of 8 sequences whose context reaches 4,096 at the end of
 the timed steps. ``value`` is decoded tokens a second with the steps running back to back on
@@ -21,7 +21,9 @@ fraction of the measured peak and its own clock samples).
 ``--design busavik`` leaves all of that aside and measures the Busavik design (latent
 attention, Dynamic Tanh, routed experts) at layer sizes of real models beside the Qwen3 model
 of equal size: prefill and decode tokens/s, and the kernels of a step by class against what
-each class must compute or read.
+each class must compute or read. ``--design fimudra`` does the same for the Fimudra design
+(residual streams, attention with a sink beside a gated matrix memory, a decaying matrix
+state, routed experts with identity experts).
 """
 import argparse
 import json
@@ -374,6 +376,86 @@ def busavik_shapes(name):
     return BusavikConfig.from_dict(doc), twin
 
 
+def fimudra_shapes(name):
+    """A Fimudra configuration whose layers have the sizes of a real model's (a parallel layer
+    and a decaying-state layer, both with routed experts) and the Qwen3 configuration of equal
+    width, head count, KV heads, head size and layer count whose feed-forward has the size of
+    the experts a token uses, the closest model of this library."""
+    from mormot2_ai_b200 import FimudraConfig, Qwen3Config
+    sizes = {
+        # width, heads, kv heads, dim, memory heads, memory dim, state heads, state dim, experts,
+        # top, identity, expert ff, shared ff
+        "small": (1024, 8, 2, 64, 4, 64, 16, 64, 16, 2, 2, 1024, 1024),
+        "mid": (2048, 16, 4, 128, 8, 128, 32, 64, 64, 6, 2, 1408, 2816),
+    }[name]
+    w, h, kv, dim, mh, md, sh, sd, ne, top, ident, eff, sff = sizes
+    vocab = 32768
+    mlp = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0},
+           "router": {"experts": ne, "identity": ident, "top": top, "scale": 1.0},
+           "shared": {"ff": sff, "limit": 7.0}}
+    doc = {"architecture": "Fimudra", "vocab": vocab, "width": w, "norm": {"eps": 1e-6},
+           "embedding": {"scale": 1.0}, "streams": 2,
+           "layers": [
+               {"type": "parallel", "mlp": mlp, "mixer": {
+                   "left": {"heads": h, "kv_heads": kv, "dim": dim, "vdim": dim,
+                            "scale": dim ** -0.5,
+                            "rot": {"base": 500000.0, "dims": dim, "scaling": {
+                                "factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+                   "right": {"heads": mh, "dim": md, "vdim": md, "gate_cap": 15.0},
+                   "left_scale": 1.0, "right_scale": 1.0}},
+               {"type": "wkv", "mlp": mlp,
+                "mixer": {"heads": sh, "dim": sd, "decay_rank": 64}}]}
+    twin = Qwen3Config(vocab_size=vocab, hidden_size=w, num_hidden_layers=2,
+                       num_attention_heads=h, num_key_value_heads=kv, head_dim=dim,
+                       intermediate_size=top * eff + sff, max_position_embeddings=40960,
+                       rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True)
+    return FimudraConfig.from_dict(doc), twin
+
+
+def fimudra_work(cfg, tokens, batch, held, experts_read=None):
+    """As ``busavik_work`` for the Fimudra family, with a class of its own for the recurrences:
+    a prefill's recurrences count the multiply-adds of the state's update and of its read
+    (4 x dim x vdim a token and head), a decode step's the state they read and write."""
+    pairs = tokens * (tokens + 1) / 2
+    out = {"prefill_flops": {"attention": 0.0, "products": 0.0, "recurrence": 0.0},
+           "decode_bytes": {"attention": 0.0, "products": 0.0, "recurrence": 0.0}}
+    w = cfg.width
+    for layer in cfg.layers:
+        m, mlp = layer["mixer"], layer["mlp"]
+        if layer["type"] == "wkv":
+            hd = m["heads"] * m["dim"]
+            rank = m.get("decay_rank") or 64
+            dense = 5 * hd * w + rank * (w + hd)
+            state = m["heads"] * m["dim"] * m["dim"]
+            rec = 4 * state
+        else:
+            l, r = m["left"], m["right"]
+            dense = (l["heads"] * l["dim"] + l["kv_heads"] * (l["dim"] + l["vdim"])
+                     + l["heads"] * l["vdim"]) * w
+            dense += (2 * r["heads"] * (r["dim"] + r["vdim"]) + 2 * r["heads"]
+                      + r["heads"] * r["vdim"]) * w
+            state = r["heads"] * (r["dim"] * r["vdim"] + r["dim"] + 1)
+            rec = 4 * r["heads"] * r["dim"] * r["vdim"]
+            out["prefill_flops"]["attention"] += 2 * l["heads"] * (l["dim"] + l["vdim"]) * pairs
+            out["decode_bytes"]["attention"] += 2 * held * l["kv_heads"] * (l["dim"] + l["vdim"])
+        ff_params = ff_read = 0
+        if mlp:
+            e, top = mlp["router"]["experts"], mlp["router"]["top"]
+            routed = e + (mlp["router"].get("identity") or 0)
+            one = 3 * w * mlp["expert"]["ff"]
+            shared = 3 * w * mlp["shared"]["ff"] if mlp.get("shared") else 0
+            ff_params = top * one + shared + routed * w
+            chosen = min(e, batch * top) if experts_read is None else experts_read
+            ff_read = chosen * one + shared + routed * w
+        out["prefill_flops"]["products"] += 2 * tokens * (dense + ff_params)
+        out["prefill_flops"]["recurrence"] += tokens * rec
+        out["decode_bytes"]["products"] += 2 * (dense + ff_read)
+        out["decode_bytes"]["recurrence"] += batch * 2 * 4 * state
+    out["prefill_flops"]["products"] += 2 * cfg.vocab * w
+    out["decode_bytes"]["products"] += 2 * cfg.vocab * w
+    return out
+
+
 def busavik_work(cfg, tokens, batch, held, experts_read=None):
     """Multiply-add work (FLOPs) of a prefill of one prompt of ``tokens`` tokens and bytes that a
     decode step of ``batch`` sequences holding ``held`` tokens together must read, by class of
@@ -381,6 +463,8 @@ def busavik_work(cfg, tokens, batch, held, experts_read=None):
     head scores rows of kv_rank + rot_dim values and sums rows of kv_rank values.
     ``experts_read``: how many different experts a decode step's tokens chose (measured; with
     random weights the tokens of a batch choose much the same ones), else the most possible."""
+    if hasattr(cfg, "streams"):
+        return fimudra_work(cfg, tokens, batch, held, experts_read)
     pairs = tokens * (tokens + 1) / 2
     out = {"prefill_flops": {"attention": 0.0, "products": 0.0},
            "decode_bytes": {"attention": 0.0, "products": 0.0}}
@@ -430,7 +514,8 @@ def busavik_bench(a):
     steps, warm = min(a.steps, 64), max(a.warmup, 3)
     points = {}
     for size in [v for v in a.sizes.split(",") if v]:
-        for family, cfg in zip(("busavik", "qwen3"), busavik_shapes(size)):
+        shapes = fimudra_shapes if a.design == "fimudra" else busavik_shapes
+        for family, cfg in zip((a.design, "qwen3"), shapes(size)):
             eng = Engine.from_random(cfg, seed=5, std=0.02, max_tokens=batch * ctx + tokens,
                                      max_context=max(ctx, tokens), max_slots=batch,
                                      prefill_chunk=4096, max_step_tokens=8192)
@@ -454,8 +539,9 @@ def busavik_bench(a):
             chosen = []
             for layer in eng.model.layers:
                 if hasattr(layer.feed_forward, "probe"):
-                    layer.feed_forward.probe = lambda part, step, ids: chosen.append(
-                        int(ids.unique().numel()))
+                    real = layer.feed_forward.experts      # ids from there on: identity experts
+                    layer.feed_forward.probe = lambda part, step, ids, real=real: chosen.append(
+                        int(ids[ids < real].unique().numel()))
             dshares = {}
             for k in range(6):
                 _, sh, _ = eng.timed_step([Entry(s, [1 + k]) for s in slots])
@@ -485,7 +571,7 @@ def busavik_bench(a):
                 "clocks": {"prefill": pclocks, "decode": dclocks}}
             del eng, sampler
             torch.cuda.empty_cache()
-    print(json.dumps({"design": "busavik", "beside": "qwen3 of equal width, heads and feed-forward",
+    print(json.dumps({"design": a.design, "beside": "qwen3 of equal width, heads and feed-forward",
                       "prefill_tokens": tokens, "decode_batch": batch, "decode_context": ctx,
                       "dtype": "bf16", "data": "synthetic", "peaks": pk, "points": points}))
     return 0
@@ -507,15 +593,15 @@ def main():
                     help="token counts of the long prefill points (one sequence each)")
     ap.add_argument("--only-prefill", type=int, nargs="?", const=PREFILL_TOKENS, default=0,
                     help="only a prefill of this many tokens (for profiles; prints a short line)")
-    ap.add_argument("--design", default="", choices=["", "busavik"],
-                    help="busavik: instead of the default workload, prefill and decode of the "
-                         "Busavik design at layer sizes of real models beside the Qwen3 model of "
+    ap.add_argument("--design", default="", choices=["", "busavik", "fimudra"],
+                    help="busavik, fimudra: instead of the default workload, prefill and decode "
+                         "of that design at layer sizes of real models beside the Qwen3 model of "
                          "equal size (prints its own JSON line)")
     ap.add_argument("--sizes", default="small,mid", help="with --design: which layer sizes")
     ap.add_argument("--busavik-prefill", type=int, default=2048)
     ap.add_argument("--busavik-context", type=int, default=2048)
     a = ap.parse_args()
-    if a.design == "busavik" and a.impl == "ours" and a.gpus == 1:
+    if a.design and a.impl == "ours" and a.gpus == 1:
         return busavik_bench(a)
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

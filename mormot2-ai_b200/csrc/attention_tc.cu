@@ -173,7 +173,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
                        int out_stride, const int* __restrict__ page_table, int max_pages,
                        int ring_pages, const int* __restrict__ seq_start,
                        const int* __restrict__ seq_past, const int* __restrict__ seq_slot, int nh,
-                       int nkv, int window, float scale_log2, int* __restrict__ error) {
+                       int nkv, int window, float scale_log2, int* __restrict__ error,
+                       const float* __restrict__ sink) {
   extern __shared__ __align__(1024) uint8_t at_smem[];
   const uint32_t raw = smem_u32(at_smem);
   if (raw & 1023u) {  // swizzled tiles need it; never seen, but a wrong result must not follow
@@ -404,6 +405,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
     // the last product done means all are (the tensor core works in the order of issue)
     mbar_wait(o_done0 + 8 * ((n_pages - 1) & 1), ((n_pages - 1) >> 1) & 1, error, 18);
     tc_fence_after_sync();
+    // a sink: one more term exp(sink[h]) in the row's denominator, against the same reference
+    // as the sums (a sink far above every score makes the sum infinite and the row zero, its
+    // limit)
+    if (sink != nullptr)
+      l += exp2f(sink[h] * 1.4426950408889634f - (m_ref == -INFINITY ? 0.f : m_ref));
     const float inv = 1.0f / l;
     // A thread holds one row of O; written from there, a warp's store would touch 32 rows with
     // 16 bytes each. Q's shared memory is free now (every product is done): the warp lays its
@@ -453,7 +459,7 @@ MB_EXPORT int mb_attention_prefill_tc(const void* q, int q_stride, int q_cols, v
                                       int ring_pages, const int* seq_start, const int* seq_past,
                                       const int* seq_slot, int B, int T, int max_new, int nh,
                                       int nkv, int hd, int window, float scale, int* error,
-                                      void* stream) {
+                                      const float* sink, void* stream) {
   if (B <= 0 || max_new <= 0) return 0;
   if (hd != AT_HD) MB_FAIL("mb_attention_prefill_tc: heads of %d values (128 only)", hd);
   if (nkv <= 0 || nh % nkv) MB_FAIL("mb_attention_prefill_tc: %d heads on %d KV heads", nh, nkv);
@@ -478,6 +484,6 @@ MB_EXPORT int mb_attention_prefill_tc(const void* q, int q_stride, int q_cols, v
   dim3 grid(nh, tiles, B);
   mb_launch(attn_prefill_tc_kernel, grid, dim3(AT_THREADS), AT_SMEM, (cudaStream_t)stream, tmQ,
             tmK, tmV, (bf16*)out, out_stride, page_table, max_pages, ring_pages, seq_start,
-            seq_past, seq_slot, nh, nkv, window, scale * 1.4426950408889634f, error);
+            seq_past, seq_slot, nh, nkv, window, scale * 1.4426950408889634f, error, sink);
   MB_CHECK_LAUNCH("mb_attention_prefill_tc");
 }

@@ -6,8 +6,8 @@
 // step's tokens of its sequence in order, sixteen at a time staged in shared memory; a thread
 // owns one value column of the head's matrix state, which is kept in shared memory.
 //
-//   token_shift   mix_s[t] = h[t] + (h[t-1] - h[t]) mu_s   for several s at once; h[-1] of a
-//                 sequence is kept in the state (zeros before the first token)
+//   token_shift   [h[t] ; h[t-1] - h[t]], from which every blend h + (h' - h) mu_s is projected
+//                 by one product; h[-1] of a sequence is kept in the state (zeros at first)
 //   wkv_scan      decay w = exp(-exp(lw + w0)); o_t = (S + diag(u) k v^T)^T r;
 //                 S <- diag(w) S + k v^T; then o / rms(o) * norm * silu(g) per head
 //   mlstm_scan    log gates i = cap tanh((zi + bi)/cap), f = logsigmoid(cap tanh((zf + bf)/cap));
@@ -18,13 +18,14 @@
 MB_DEFINE_LAST_ERROR
 
 // ------------------------------------------------------------------ token shift
+// out[t] = [h[t] ; h[t-1] - h[t]] (2 W values): a projection of a blend h + (h' - h) mu is then
+// ONE product of this row with the weight [W_s | W_s diag(mu_s)], for all blends s at once.
 template <typename T>
 __global__ void token_shift_kernel(const T* __restrict__ h, const float* __restrict__ state,
                                    size_t state_stride, size_t state_off,
                                    const int* __restrict__ tok_seq,
                                    const int* __restrict__ seq_start,
-                                   const int* __restrict__ seq_slot, const float* __restrict__ mu,
-                                   int n_mix, T* __restrict__ out, int Ttok, int W) {
+                                   const int* __restrict__ seq_slot, T* __restrict__ out, int W) {
   mb_grid_wait();
   mb_grid_launch_next();
   const int t = blockIdx.x;
@@ -32,29 +33,27 @@ __global__ void token_shift_kernel(const T* __restrict__ h, const float* __restr
   const bool first = seq_start[b] == t;
   const float* prev_state = state + (size_t)seq_slot[b] * state_stride + state_off;
   for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    const float hv = to_f32<T>(h[(size_t)t * W + c]);
+    const T hv = h[(size_t)t * W + c];
     const float pv = first ? prev_state[c] : to_f32<T>(h[(size_t)(t - 1) * W + c]);
-    const float d = pv - hv;
-    for (int s = 0; s < n_mix; ++s)
-      out[((size_t)s * Ttok + t) * W + c] = from_f32<T>(fmaf(d, mu[(size_t)s * W + c], hv));
+    out[(size_t)t * 2 * W + c] = hv;
+    out[(size_t)t * 2 * W + W + c] = from_f32<T>(pv - to_f32<T>(hv));
   }
 }
 
 MB_EXPORT int mb_token_shift(const void* h, int dtype, const float* state, long long state_stride,
                              long long state_off, const int* tok_seq, const int* seq_start,
-                             const int* seq_slot, const float* mu, int n_mix, void* out, int T,
-                             int W, void* stream) {
+                             const int* seq_slot, void* out, int T, int W, void* stream) {
   if (T <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = W >= 1024 ? 256 : 128;
   if (dtype == MB_F32)
     mb_launch(token_shift_kernel<float>, dim3(T), dim3(threads), 0, s, (const float*)h, state,
-              (size_t)state_stride, (size_t)state_off, tok_seq, seq_start, seq_slot, mu, n_mix,
-              (float*)out, T, W);
+              (size_t)state_stride, (size_t)state_off, tok_seq, seq_start, seq_slot,
+              (float*)out, W);
   else
     mb_launch(token_shift_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, s,
               (const __nv_bfloat16*)h, state, (size_t)state_stride, (size_t)state_off, tok_seq,
-              seq_start, seq_slot, mu, n_mix, (__nv_bfloat16*)out, T, W);
+              seq_start, seq_slot, (__nv_bfloat16*)out, W);
   MB_CHECK_LAUNCH("mb_token_shift");
 }
 
@@ -66,8 +65,11 @@ MB_EXPORT int mb_token_shift(const void* h, int dtype, const float* state, long 
 
 // r, k, v, lw, g: float32 [T, ld] each (head hd's values at column hd * D + i); w0, u, normw:
 // float32 [H * D]. State of a slot: [W values of the last h | H x D x D]. out [T, H * D].
-template <typename T>
-__global__ void wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ k,
+// R > 0: a thread keeps its share of a state column (R rows at most) in registers, and shared
+// memory only carries the staged tokens; R = 0: the state lies in shared memory (heads too
+// large for the registers of 512 threads).
+template <typename T, int R>
+__global__ void __launch_bounds__(512) wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ k,
                                 const float* __restrict__ v, const float* __restrict__ lw,
                                 const float* __restrict__ g, int ld,
                                 const float* __restrict__ w0, const float* __restrict__ u,
@@ -81,23 +83,36 @@ __global__ void wkv_scan_kernel(const float* __restrict__ r, const float* __rest
   extern __shared__ __align__(16) float wk_smem[];
   const int DD = (D * D + 3) & ~3;
   float* S = wk_smem;                        // [D][D], S[i * D + j]: key channel i, value channel j
-  float4* vec = (float4*)(S + DD);           // [CT][D]: r, k, decay, u * k
-  float* sv = (float*)(vec + SCAN_CT * D);   // [CT][D] v
+  float4* vec = (float4*)(S + (R > 0 ? 0 : DD));   // [CT][D]: r, k, decay, u * k
+  float* sv = (float*)(vec + SCAN_CT * D + 64);   // [CT][D] v (64 entries of room behind vec:
+                                                  // a thread may read past its last row)
   float* sg = sv + SCAN_CT * D;              // [CT][D] g
-  float* so = sg + SCAN_CT * D;              // [CT][D] o
-  const int b = blockIdx.x, hd = blockIdx.y, j = threadIdx.x;
-  const int warp = j >> 5, lane = j & 31, warps = blockDim.x >> 5;
+  float* so = sg + SCAN_CT * D;              // [CT][P][D] o, the sums over each part's channels
+  const int b = blockIdx.x, hd = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  // P groups of threads share the key channels of a column: thread (part, j) owns rows
+  // i0 .. i1 of column j of the state
+  const int Dp = (D + 31) & ~31, P = blockDim.x / Dp;
+  const int part = threadIdx.x / Dp, j = threadIdx.x - part * Dp;
+  const int per = (D + P - 1) / P, i0 = min(D, part * per), i1 = min(D, i0 + per);
+  const int cnt = i1 - i0;
   const int t0 = seq_start[b], n = seq_start[b + 1] - t0;
   float* st = state + (size_t)seq_slot[b] * state_stride + state_off;
   float* Sg = st + W + (size_t)hd * D * D;
-  for (int e = j; e < D * D; e += blockDim.x) S[e] = Sg[e];
   const bool own = j < D;
+  float Sr[R > 0 ? R : 1];
+  if (R > 0) {
+#pragma unroll
+    for (int q = 0; q < (R > 0 ? R : 1); ++q) Sr[q] = (own && i0 + q < i1) ? Sg[(i0 + q) * D + j] : 0.f;
+  } else {
+    for (int e = threadIdx.x; e < D * D; e += blockDim.x) S[e] = Sg[e];
+  }
   const int col = hd * D + j;
   const float w0j = own ? w0[col] : 0.f, uj = own ? u[col] : 0.f;
   for (int c0 = 0; c0 < n; c0 += SCAN_CT) {
     const int cn = min(SCAN_CT, n - c0);
     if (own) {
-      for (int tt = 0; tt < cn; ++tt) {
+      for (int tt = part; tt < cn; tt += P) {
         const size_t at = (size_t)(t0 + c0 + tt) * ld + col;
         const float kj = k[at];
         vec[tt * D + j] = make_float4(r[at], kj, expf(-expf(lw[at] + w0j)), uj * kj);
@@ -111,35 +126,97 @@ __global__ void wkv_scan_kernel(const float* __restrict__ r, const float* __rest
         const float vj = sv[tt * D + j];
         const float4* x = vec + tt * D;
         float o = 0.f;
-        for (int i = 0; i < D; ++i) {
-          const float4 xi = x[i];
-          const float s = S[i * D + j];
-          o = fmaf(xi.x, fmaf(xi.w, vj, s), o);
-          S[i * D + j] = fmaf(xi.z, s, xi.y * vj);
+        if (R > 0) {
+          float o4[4] = {0.f, 0.f, 0.f, 0.f};     // four sums side by side: shorter chains
+#pragma unroll
+          for (int q = 0; q < (R > 0 ? R : 1); ++q) {
+            // no branch: rows past this thread's last are read (they exist) and left out
+            const float4 xi = x[i0 + q];
+            const float sc = Sr[q];
+            const float with = fmaf(xi.x, fmaf(xi.w, vj, sc), o4[q & 3]);
+            o4[q & 3] = q < cnt ? with : o4[q & 3];
+            Sr[q] = fmaf(xi.z, sc, xi.y * vj);
+          }
+          o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+        } else {
+          // eight rows at a time: their loads are asked for together, then the multiply-adds,
+          // then the stores (written one by one a store would hold the next load back)
+          for (int ib = i0; ib < i1; ib += 8) {
+            float4 xi[8];
+            float sc[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const int i = min(ib + q, i1 - 1);
+              xi[q] = x[i];
+              sc[q] = S[i * D + j];
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              if (ib + q < i1) {
+                o = fmaf(xi[q].x, fmaf(xi[q].w, vj, sc[q]), o);
+                S[(ib + q) * D + j] = fmaf(xi[q].z, sc[q], xi[q].y * vj);
+              }
+            }
+          }
         }
-        so[tt * D + j] = o;
+        so[(tt * P + part) * D + j] = o;
       }
     }
     __syncthreads();
     for (int tt = warp; tt < cn; tt += warps) {
+      float ov[8];     // heads of up to 256 values a lane's eight; beyond, the sums are formed again
       float ss = 0.f;
-      for (int i = lane; i < D; i += 32) ss = fmaf(so[tt * D + i], so[tt * D + i], ss);
+      for (int i = lane, q = 0; i < D; i += 32, ++q) {
+        float o = 0.f;
+        for (int pp = 0; pp < P; ++pp) o += so[(tt * P + pp) * D + i];
+        if (q < 8) ov[q] = o;
+        ss = fmaf(o, o, ss);
+      }
       const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
       T* orow = out + (size_t)(t0 + c0 + tt) * H * D + hd * D;
-      for (int i = lane; i < D; i += 32) {
+      for (int i = lane, q = 0; i < D; i += 32, ++q) {
+        float o = 0.f;
+        if (q < 8) {
+          o = ov[q];
+        } else {
+          for (int pp = 0; pp < P; ++pp) o += so[(tt * P + pp) * D + i];
+        }
         const float gi = sg[tt * D + i];
-        orow[i] = from_f32<T>(so[tt * D + i] * inv * normw[hd * D + i] * (gi / (1.0f + expf(-gi))));
+        orow[i] = from_f32<T>(o * inv * normw[hd * D + i] * (gi / (1.0f + expf(-gi))));
       }
     }
     __syncthreads();
   }
-  for (int e = j; e < D * D; e += blockDim.x) Sg[e] = S[e];
+  if (R > 0) {
+#pragma unroll
+    for (int q = 0; q < (R > 0 ? R : 1); ++q)
+      if (own && i0 + q < i1) Sg[(i0 + q) * D + j] = Sr[q];
+  } else {
+    for (int e = threadIdx.x; e < D * D; e += blockDim.x) Sg[e] = S[e];
+  }
   if (hd == 0 && n > 0)
-    for (int c = j; c < W; c += blockDim.x) st[c] = to_f32<T>(h[(size_t)(t0 + n - 1) * W + c]);
+    for (int c = threadIdx.x; c < W; c += blockDim.x)
+      st[c] = to_f32<T>(h[(size_t)(t0 + n - 1) * W + c]);
+}
+
+// how many groups of threads share a column's key channels: as many as keep a block within
+// 512 threads, at most 8
+static int scan_parts(int columns) {
+  const int cp = (columns + 31) / 32 * 32;
+  int p = 512 / cp;
+  return p < 1 ? 1 : (p > 8 ? 8 : p);
+}
+
+// the rows of a state column that one thread has: 8, 16, 32 or 64 in registers, 0: more, the
+// state stays in shared memory
+static int scan_rows(int D, int columns) {
+  const int P = scan_parts(columns), per = (D + P - 1) / P;
+  return per <= 8 ? 8 : per <= 16 ? 16 : per <= 32 ? 32 : per <= 64 ? 64 : 0;
 }
 
 static size_t wkv_smem_bytes(int D) {
-  return ((size_t)((D * D + 3) & ~3) + (size_t)SCAN_CT * D * 7) * sizeof(float);
+  const size_t state = scan_rows(D, D) ? 0 : (size_t)((D * D + 3) & ~3);
+  return (state + (size_t)SCAN_CT * D * (6 + scan_parts(D)) + 64 * 4) * sizeof(float);
 }
 
 MB_EXPORT int mb_wkv_scan(const float* r, const float* k, const float* v, const float* lw,
@@ -150,23 +227,33 @@ MB_EXPORT int mb_wkv_scan(const float* r, const float* k, const float* v, const 
                           int D, void* stream) {
   if (B <= 0) return 0;
   const size_t smem = wkv_smem_bytes(D);
-  if (D <= 0 || D > 1024 || smem > 200 * 1024)
-    MB_FAIL("mb_wkv_scan: heads of %d values (the state of a head must fit 200 KB)", D);
+  if (D <= 0 || D > 512 || smem > 200 * 1024)
+    MB_FAIL("mb_wkv_scan: heads of %d values (at most 512, and what a block stages must fit "
+            "200 KB)", D);
   cudaStream_t s = (cudaStream_t)stream;
-  const int threads = (D + 31) / 32 * 32;
-#define GO(T_)                                                                                 \
+  const int threads = (D + 31) / 32 * 32 * scan_parts(D);
+#define GO(T_, R_)                                                                             \
   {                                                                                            \
     static size_t configured = 48 * 1024;                                                      \
     if (smem > configured) {                                                                   \
-      cudaFuncSetAttribute(wkv_scan_kernel<T_>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
-                           200 * 1024);                                                        \
+      cudaFuncSetAttribute(wkv_scan_kernel<T_, R_>,                                            \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);           \
       configured = 200 * 1024;                                                                 \
     }                                                                                          \
-    mb_launch(wkv_scan_kernel<T_>, dim3(B, H), dim3(threads), smem, s, r, k, v, lw, g, ld, w0, \
-              u, normw, eps, state, (size_t)state_stride, (size_t)state_off, (const T_*)h, W,  \
-              seq_start, seq_slot, (T_*)out, H, D);                                            \
+    mb_launch(wkv_scan_kernel<T_, R_>, dim3(B, H), dim3(threads), smem, s, r, k, v, lw, g, ld, \
+              w0, u, normw, eps, state, (size_t)state_stride, (size_t)state_off, (const T_*)h, \
+              W, seq_start, seq_slot, (T_*)out, H, D);                                         \
   }
-  if (dtype == MB_F32) GO(float) else GO(__nv_bfloat16)
+#define GOR(T_)                                                                                \
+  switch (scan_rows(D, D)) {                                                                   \
+    case 8: GO(T_, 8) break;                                                                   \
+    case 16: GO(T_, 16) break;                                                                 \
+    case 32: GO(T_, 32) break;                                                                 \
+    case 64: GO(T_, 64) break;                                                                 \
+    default: GO(T_, 0)                                                                         \
+  }
+  if (dtype == MB_F32) GOR(float) else GOR(__nv_bfloat16)
+#undef GOR
 #undef GO
   MB_CHECK_LAUNCH("mb_wkv_scan");
 }
@@ -180,8 +267,8 @@ __device__ __forceinline__ float log_sigmoid(float x) {
   return fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
 }
 
-template <typename T>
-__global__ void mlstm_scan_kernel(const float* __restrict__ z, int ld, int cq, int ck, int cv,
+template <typename T, int R>
+__global__ void __launch_bounds__(512) mlstm_scan_kernel(const float* __restrict__ z, int ld, int cq, int ck, int cv,
                                   int cg, int ci, int cf, const float* __restrict__ bi,
                                   const float* __restrict__ bf, float cap, float q_scale,
                                   const float* __restrict__ normw, float eps,
@@ -194,43 +281,71 @@ __global__ void mlstm_scan_kernel(const float* __restrict__ z, int ld, int cq, i
   extern __shared__ __align__(16) float ml_smem[];
   const int DD = (D * DV + 3) & ~3;
   float* S = ml_smem;                          // [D][DV]
-  float2* qk = (float2*)(S + DD);              // [CT][D]: q (scaled), k
-  float* sv = (float*)(qk + SCAN_CT * D);      // [CT][DV] v
+  float2* qk = (float2*)(S + (R > 0 ? 0 : DD));   // [CT][D]: q (scaled), k
+  float* sv = (float*)(qk + SCAN_CT * D + 64); // [CT][DV] v (64 entries of room behind qk)
   float* sg = sv + SCAN_CT * DV;               // [CT][DV] the output gate's logit
-  float* snum = sg + SCAN_CT * DV;             // [CT][DV] S^T q
-  float* snq = snum + SCAN_CT * DV;            // [CT][D] n_i q_i
+  float* snq = sg + SCAN_CT * DV;              // [CT][D] n_i q_i
   float* sab = snq + SCAN_CT * D;              // [CT][4]: the state's factor, the input's, e^(-m)
-  const int b = blockIdx.x, hd = blockIdx.y, j = threadIdx.x;
-  const int warp = j >> 5, lane = j & 31, warps = blockDim.x >> 5;
+  float* snum = sab + SCAN_CT * 4;             // [CT][P][DV] S^T q, summed over each part's rows
+  const int b = blockIdx.x, hd = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  // P groups of threads share the key channels of a column, as in wkv_scan_kernel
+  const int Cp = ((D > DV ? D : DV) + 31) & ~31, P = blockDim.x / Cp;
+  const int part = threadIdx.x / Cp, j = threadIdx.x - part * Cp;
+  const int per = (D + P - 1) / P, i0 = min(D, part * per), i1 = min(D, i0 + per);
+  const int cnt = i1 - i0;
   const int t0 = seq_start[b], n = seq_start[b + 1] - t0;
   float* st = state + (size_t)seq_slot[b] * state_stride + state_off +
               (size_t)hd * ((size_t)D * DV + D + 1);
-  for (int e = j; e < D * DV; e += blockDim.x) S[e] = st[e];
-  const bool own_k = j < D, own_v = j < DV;
+  const bool own_k = j < D && part == 0, own_v = j < DV;
+  float Sr[R > 0 ? R : 1];
+  if (R > 0) {
+#pragma unroll
+    for (int q = 0; q < (R > 0 ? R : 1); ++q)
+      Sr[q] = (own_v && i0 + q < i1) ? st[(size_t)(i0 + q) * DV + j] : 0.f;
+  } else {
+    for (int e = threadIdx.x; e < D * DV; e += blockDim.x) S[e] = st[e];
+  }
   float nj = own_k ? st[(size_t)D * DV + j] : 0.f;
-  float m = st[(size_t)D * DV + D];          // thread 0's copy is the one that counts
+  float m = st[(size_t)D * DV + D];          // the last thread's copy is the one that counts
   const float bih = bi[hd], bfh = bf[hd];
   for (int c0 = 0; c0 < n; c0 += SCAN_CT) {
     const int cn = min(SCAN_CT, n - c0);
-    for (int tt = 0; tt < cn; ++tt) {
+    for (int tt = part; tt < cn; tt += P) {
       const float* zr = z + (size_t)(t0 + c0 + tt) * ld;
-      if (own_k) qk[tt * D + j] = make_float2(zr[cq + hd * D + j] * q_scale, zr[ck + hd * D + j]);
+      if (j < D) qk[tt * D + j] = make_float2(zr[cq + hd * D + j] * q_scale, zr[ck + hd * D + j]);
       if (own_v) {
         sv[tt * DV + j] = zr[cv + hd * DV + j];
         sg[tt * DV + j] = zr[cg + hd * DV + j];
       }
     }
-    if (j == 0) {
-      // the gates and the running maximum, token after token
-      for (int tt = 0; tt < cn; ++tt) {
-        const float* zr = z + (size_t)(t0 + c0 + tt) * ld;
-        const float gi = cap * tanhf((zr[ci + hd] + bih) / cap);
-        const float gf = log_sigmoid(cap * tanhf((zr[cf + hd] + bfh) / cap));
-        const float m_new = fmaxf(gf + m, gi);
-        sab[tt * 4] = expf(gf + m - m_new);
-        sab[tt * 4 + 1] = expf(gi - m_new);
-        sab[tt * 4 + 2] = expf(-m_new);
-        m = m_new;
+    if (warp == warps - 1) {
+      // the gates by the last warp: every token's two logarithms side by side (a lane a
+      // token), then the running maximum token after token by one lane (additions and maxima
+      // only), then the exponentials side by side again
+      float gi = 0.f, gf = 0.f;
+      if (lane < cn) {
+        const float* zr = z + (size_t)(t0 + c0 + lane) * ld;
+        gi = cap * tanhf((zr[ci + hd] + bih) / cap);
+        gf = log_sigmoid(cap * tanhf((zr[cf + hd] + bfh) / cap));
+        sab[lane * 4] = gi;
+        sab[lane * 4 + 1] = gf;
+      }
+      __syncwarp();
+      if (lane == 31) {
+        for (int tt = 0; tt < cn; ++tt) {
+          const float m_new = fmaxf(sab[tt * 4 + 1] + m, sab[tt * 4]);
+          sab[tt * 4 + 2] = m;          // the maximum before this token
+          sab[tt * 4 + 3] = m_new;
+          m = m_new;
+        }
+      }
+      __syncwarp();
+      if (lane < cn) {
+        const float m_old = sab[lane * 4 + 2], m_new = sab[lane * 4 + 3];
+        sab[lane * 4] = expf(gf + m_old - m_new);
+        sab[lane * 4 + 1] = expf(gi - m_new);
+        sab[lane * 4 + 2] = expf(-m_new);
       }
     }
     __syncthreads();
@@ -245,39 +360,84 @@ __global__ void mlstm_scan_kernel(const float* __restrict__ z, int ld, int cq, i
         const float bv = bb * sv[tt * DV + j];
         const float2* x = qk + tt * D;
         float num = 0.f;
-        for (int i = 0; i < D; ++i) {
-          const float2 xi = x[i];
-          const float s = fmaf(a, S[i * DV + j], xi.y * bv);
-          S[i * DV + j] = s;
-          num = fmaf(s, xi.x, num);
+        if (R > 0) {
+          float n4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int q = 0; q < (R > 0 ? R : 1); ++q) {
+            const float2 xi = x[i0 + q];      // no branch, as in wkv_scan_kernel
+            const float s = fmaf(a, Sr[q], xi.y * bv);
+            Sr[q] = s;
+            const float with = fmaf(s, xi.x, n4[q & 3]);
+            n4[q & 3] = q < cnt ? with : n4[q & 3];
+          }
+          num = (n4[0] + n4[1]) + (n4[2] + n4[3]);
+        } else {
+          for (int ib = i0; ib < i1; ib += 8) {     // eight rows at a time, as in wkv_scan_kernel
+            float2 xi[8];
+            float sc[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const int i = min(ib + q, i1 - 1);
+              xi[q] = x[i];
+              sc[q] = S[i * DV + j];
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              if (ib + q < i1) {
+                const float s = fmaf(a, sc[q], xi[q].y * bv);
+                S[(ib + q) * DV + j] = s;
+                num = fmaf(s, xi[q].x, num);
+              }
+            }
+          }
         }
-        snum[tt * DV + j] = num;
+        snum[(tt * P + part) * DV + j] = num;
       }
     }
     __syncthreads();
     for (int tt = warp; tt < cn; tt += warps) {
+      float nv[8];     // value rows of up to 256 a lane's eight; beyond, the sums are formed again
       float nq = 0.f, ss = 0.f;
       for (int i = lane; i < D; i += 32) nq += snq[tt * D + i];
-      for (int i = lane; i < DV; i += 32) ss = fmaf(snum[tt * DV + i], snum[tt * DV + i], ss);
+      for (int i = lane, q = 0; i < DV; i += 32, ++q) {
+        float num = 0.f;
+        for (int pp = 0; pp < P; ++pp) num += snum[(tt * P + pp) * DV + i];
+        if (q < 8) nv[q] = num;
+        ss = fmaf(num, num, ss);
+      }
       nq = warp_sum(nq);
       ss = warp_sum(ss);
       const float den = fmaxf(fabsf(nq), sab[tt * 4 + 2]) + 1e-6f;
       const float inv = 1.0f / sqrtf(ss / (den * den) / (float)DV + eps);
       T* orow = out + (size_t)(t0 + c0 + tt) * H * DV + hd * DV;
-      for (int i = lane; i < DV; i += 32) {
+      for (int i = lane, q = 0; i < DV; i += 32, ++q) {
+        float num = 0.f;
+        if (q < 8) {
+          num = nv[q];
+        } else {
+          for (int pp = 0; pp < P; ++pp) num += snum[(tt * P + pp) * DV + i];
+        }
         const float gate = 1.0f / (1.0f + expf(-sg[tt * DV + i]));
-        orow[i] = from_f32<T>(snum[tt * DV + i] / den * inv * normw[hd * DV + i] * gate);
+        orow[i] = from_f32<T>(num / den * inv * normw[hd * DV + i] * gate);
       }
     }
     __syncthreads();
   }
-  for (int e = j; e < D * DV; e += blockDim.x) st[e] = S[e];
+  if (R > 0) {
+#pragma unroll
+    for (int q = 0; q < (R > 0 ? R : 1); ++q)
+      if (own_v && i0 + q < i1) st[(size_t)(i0 + q) * DV + j] = Sr[q];
+  } else {
+    for (int e = threadIdx.x; e < D * DV; e += blockDim.x) st[e] = S[e];
+  }
   if (own_k) st[(size_t)D * DV + j] = nj;
-  if (j == 0) st[(size_t)D * DV + D] = m;
+  if (threadIdx.x == blockDim.x - 1) st[(size_t)D * DV + D] = m;
 }
 
 static size_t mlstm_smem_bytes(int D, int DV) {
-  return ((size_t)((D * DV + 3) & ~3) + (size_t)SCAN_CT * (3 * D + 3 * DV + 4)) * sizeof(float);
+  const int P = scan_parts(D > DV ? D : DV);
+  const size_t state = scan_rows(D, D > DV ? D : DV) ? 0 : (size_t)((D * DV + 3) & ~3);
+  return (state + (size_t)SCAN_CT * (3 * D + (2 + P) * DV + 4) + 64 * 2) * sizeof(float);
 }
 
 MB_EXPORT int mb_mlstm_scan(const float* z, int ld, int cq, int ck, int cv, int cg, int ci, int cf,
@@ -287,47 +447,63 @@ MB_EXPORT int mb_mlstm_scan(const float* z, int ld, int cq, int ck, int cv, int 
                             void* out, int dtype, int B, int H, int D, int DV, void* stream) {
   if (B <= 0) return 0;
   const size_t smem = mlstm_smem_bytes(D, DV);
-  if (D <= 0 || DV <= 0 || D > 1024 || DV > 1024 || smem > 200 * 1024)
-    MB_FAIL("mb_mlstm_scan: heads of %d x %d values (the state of a head must fit 200 KB)", D, DV);
+  if (D <= 0 || DV <= 0 || D > 512 || DV > 512 || smem > 200 * 1024)
+    MB_FAIL("mb_mlstm_scan: heads of %d x %d values (at most 512 each, and what a block stages "
+            "must fit 200 KB)", D, DV);
   cudaStream_t s = (cudaStream_t)stream;
-  const int threads = ((D > DV ? D : DV) + 31) / 32 * 32;
-#define GO(T_)                                                                                 \
+  const int threads = ((D > DV ? D : DV) + 31) / 32 * 32 * scan_parts(D > DV ? D : DV);
+#define GO(T_, R_)                                                                             \
   {                                                                                            \
     static size_t configured = 48 * 1024;                                                      \
     if (smem > configured) {                                                                   \
-      cudaFuncSetAttribute(mlstm_scan_kernel<T_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                           200 * 1024);                                                        \
+      cudaFuncSetAttribute(mlstm_scan_kernel<T_, R_>,                                          \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);           \
       configured = 200 * 1024;                                                                 \
     }                                                                                          \
-    mb_launch(mlstm_scan_kernel<T_>, dim3(B, H), dim3(threads), smem, s, z, ld, cq, ck, cv, cg, \
-              ci, cf, bi, bf, cap, q_scale, normw, eps, state, (size_t)state_stride,           \
+    mb_launch(mlstm_scan_kernel<T_, R_>, dim3(B, H), dim3(threads), smem, s, z, ld, cq, ck, cv, \
+              cg, ci, cf, bi, bf, cap, q_scale, normw, eps, state, (size_t)state_stride,       \
               (size_t)state_off, seq_start, seq_slot, (T_*)out, H, D, DV);                     \
   }
-  if (dtype == MB_F32) GO(float) else GO(__nv_bfloat16)
+#define GOR(T_)                                                                                \
+  switch (scan_rows(D, D > DV ? D : DV)) {                                                     \
+    case 8: GO(T_, 8) break;                                                                   \
+    case 16: GO(T_, 16) break;                                                                 \
+    case 32: GO(T_, 32) break;                                                                 \
+    case 64: GO(T_, 64) break;                                                                 \
+    default: GO(T_, 0)                                                                         \
+  }
+  if (dtype == MB_F32) GOR(float) else GOR(__nv_bfloat16)
+#undef GOR
 #undef GO
   MB_CHECK_LAUNCH("mb_mlstm_scan");
 }
 
 // ------------------------------------------------------------------ tanh between two products
 template <typename T>
-__global__ void tanh_kernel(const float* __restrict__ in, T* __restrict__ out, size_t total) {
+__global__ void tanh_kernel(const float* __restrict__ in, int ld_in, T* __restrict__ out,
+                            int rows, int cols) {
   mb_grid_wait();
   mb_grid_launch_next();
+  const size_t total = (size_t)rows * cols;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
-       i += (size_t)gridDim.x * blockDim.x)
-    out[i] = from_f32<T>(tanhf(in[i]));
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / cols, c = i - r * cols;
+    out[i] = from_f32<T>(tanhf(in[r * ld_in + c]));
+  }
 }
 
-// out = tanh(in) for `total` float32 values, rounded to the activation type.
-MB_EXPORT int mb_tanh(const float* in, void* out, int out_dtype, long long total, void* stream) {
-  if (total <= 0) return 0;
-  const long long want = (total + 255) / 256;
+// out [rows, cols] = tanh(in [rows, cols] float32 with a row pitch of ld_in), rounded to the
+// activation type.
+MB_EXPORT int mb_tanh(const float* in, int ld_in, void* out, int out_dtype, int rows, int cols,
+                      void* stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  const long long want = ((long long)rows * cols + 255) / 256;
   const dim3 grid((unsigned)(want < 148 * 8 ? want : 148 * 8));
   if (out_dtype == MB_F32)
-    mb_launch(tanh_kernel<float>, grid, dim3(256), 0, (cudaStream_t)stream, in, (float*)out,
-              (size_t)total);
+    mb_launch(tanh_kernel<float>, grid, dim3(256), 0, (cudaStream_t)stream, in, ld_in,
+              (float*)out, rows, cols);
   else
-    mb_launch(tanh_kernel<__nv_bfloat16>, grid, dim3(256), 0, (cudaStream_t)stream, in,
-              (__nv_bfloat16*)out, (size_t)total);
+    mb_launch(tanh_kernel<__nv_bfloat16>, grid, dim3(256), 0, (cudaStream_t)stream, in, ld_in,
+              (__nv_bfloat16*)out, rows, cols);
   MB_CHECK_LAUNCH("mb_tanh");
 }

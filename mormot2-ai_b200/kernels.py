@@ -376,30 +376,25 @@ def add_scaled(x: torch.Tensor, terms, store: bool = False) -> None:
 
 
 # ------------------------------------------------------------------------------ recurrences
-def token_shift(h: torch.Tensor, state: torch.Tensor, step, mu: torch.Tensor,
-                out: torch.Tensor) -> None:
-    """out[s, t] = h[t] + (h[t-1] - h[t]) * mu[s] for every s; the row before a sequence's
-    first row of this step is read from its state (``state`` [slots, >= W] float32, a view
-    whose rows may lie apart)."""
+def token_shift(h: torch.Tensor, state: torch.Tensor, step, out: torch.Tensor) -> None:
+    """out[t] = [h[t] ; h[t-1] - h[t]]; the row before a sequence's first row of this step is
+    read from its state (``state`` [slots, >= W] float32, a view whose rows may lie apart)."""
     T, W = h.shape
-    n = mu.shape[0]
-    state_off = 0
-    _contig(h, "h"), _contig(out, "out"), _contig(mu, "mu")
-    assert state.stride(1) == 1
-    assert out.shape == (n, T, W) and out.dtype == h.dtype and mu.shape == (n, W)
-    assert mu.dtype == torch.float32 and state.dtype == torch.float32
+    _contig(h, "h"), _contig(out, "out")
+    assert out.shape == (T, 2 * W) and out.dtype == h.dtype
+    assert state.dtype == torch.float32 and state.stride(1) == 1 and state.shape[1] >= W
     _call("recurrent", "mb_token_shift",
-          [_vp, _i, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _vp],
-          _ptr(h), code_of(h.dtype), _ptr(state), state.stride(0), state_off, _ptr(step.tok_seq),
-          _ptr(step.seq_start), _ptr(step.seq_slot), _ptr(mu), n, _ptr(out), T, W, _stream())
+          [_vp, _i, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _i, _i, _vp],
+          _ptr(h), code_of(h.dtype), _ptr(state), state.stride(0), 0, _ptr(step.tok_seq),
+          _ptr(step.seq_start), _ptr(step.seq_slot), _ptr(out), T, W, _stream())
 
 
 def tanh_rows(x: torch.Tensor, out: torch.Tensor) -> None:
-    """out = tanh(x): float32 in, the activation type out."""
-    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
-    assert x.numel() == out.numel()
-    _call("recurrent", "mb_tanh", [_vp, _vp, _i, _ll, _vp], _ptr(x), _ptr(out),
-          code_of(out.dtype), x.numel(), _stream())
+    """out = tanh(x): float32 rows in (they may lie apart), the activation type out."""
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and out.is_contiguous()
+    assert x.shape == out.shape
+    _call("recurrent", "mb_tanh", [_vp, _i, _vp, _i, _i, _i, _vp], _ptr(x), x.stride(0),
+          _ptr(out), code_of(out.dtype), x.shape[0], x.shape[1], _stream())
 
 
 def wkv_scan(r, k, v, lw, g, w0, u, normw, eps: float, state: torch.Tensor,
@@ -843,7 +838,8 @@ def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, l
 
 
 def attention_prefill_tc(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh, nkv,
-                         hd, window: int, scale: float, error: torch.Tensor) -> None:
+                         hd, window: int, scale: float, error: torch.Tensor,
+                         sink: Optional[torch.Tensor] = None) -> None:
     """The prefill attention on tcgen05 (heads of 128 values): S and O in tensor memory, Q, K
     and V tiles by TMA."""
     _contig(out, "out")
@@ -851,8 +847,8 @@ def attention_prefill_tc(q: torch.Tensor, q_stride: int, out: torch.Tensor, step
     pool_rows = line.k.shape[0] * line.k.shape[1] * line.k.shape[2]
     _call("attention_tc", "mb_attention_prefill_tc",
           [_vp, _i, _i, _vp, _i, _vp, _vp, _ll, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
-           _i, _i, _f, _vp, _vp],
+           _i, _i, _f, _vp, _vp, _vp],
           _ptr(q), q_stride, nh * hd, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
           pool_rows, _ptr(line.page_table), line.max_pages, line.ring_pages,
           _ptr(step.seq_start), _ptr(step.seq_past), _ptr(step.seq_slot), step.B, q.shape[0],
-          step.max_new, nh, nkv, hd, window, float(scale), _ptr(error), _stream())
+          step.max_new, nh, nkv, hd, window, float(scale), _ptr(error), _ptr(sink), _stream())

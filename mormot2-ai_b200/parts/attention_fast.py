@@ -47,8 +47,7 @@ def decode_many_splits(step, nh: int, nkv: int, sms: int) -> int:
 
 def run(rt, q, q_stride, out, step, line, nh, nkv, hd, window, scale, sink=None) -> bool:
     """True if a fast kernel took the call; False: the caller uses the general kernel.
-    ``sink``: float32 [nh], one more term exp(sink[h]) in every softmax denominator; the
-    ``mma.sync`` kernels take it (the tcgen05 prefill kernel does not)."""
+    ``sink``: float32 [nh], one more term exp(sink[h]) in every softmax denominator."""
     if hd not in FAST_HEAD_DIMS or q.dtype != torch.bfloat16 or q_stride % 8 or q.data_ptr() % 16:
         return False
     if step.decode:
@@ -63,10 +62,10 @@ def run(rt, q, q_stride, out, step, line, nh, nkv, hd, window, scale, sink=None)
         return True
     if out.stride(0) % 8 or out.data_ptr() % 16:
         return False
-    if hd == 128 and q.stride(1) == 1 and sink is None:
+    if hd == 128 and q.stride(1) == 1:
         # S and O in tensor memory, tiles by TMA (csrc/attention_tc.cu)
         K.attention_prefill_tc(q, q_stride, out, step, line, nh, nkv, hd, window, scale,
-                               rt.error_word)
+                               rt.error_word, sink)
         return True
     K.attention_prefill(q, q_stride, out, step, line, nh, nkv, hd, window, scale,
                         rt.error_word, sink)

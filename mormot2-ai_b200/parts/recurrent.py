@@ -4,7 +4,8 @@ written when it ends; everything that enters the recurrence is float32 on both p
 projections' operands are of the activation type, their sums float32).
 
 ``wkv`` — token-shifted time mixing with a decaying matrix state per head. With h' the row
-before (zeros before a sequence's first), each of r, k, v, g, w reads h + (h' − h) · mu_s;
+before (zeros before a sequence's first), each of r, k, v, g, w reads h + (h' − h) · mu_s
+(computed as ONE product [W_s | W_s diag(mu_s)] · [h ; h' − h] for all five);
 r, k, v = W_r, W_k, W_v of their mixes (heads × dim), gate = silu(W_g ·), decay
 w = exp(−exp(W_w2 tanh(W_w1 ·) + w0)) per head and key channel;
 o_t = (S + diag(u) k vᵀ)ᵀ r, S ← diag(w) S + k vᵀ; each head's o over its root mean square,
@@ -29,6 +30,22 @@ from .base import MIXERS, Part, StateNeed, TensorNeed
 from .linear import Linear
 
 
+def _scan_parts(columns: int) -> int:
+    """How many groups of threads share a state column's rows (csrc/recurrent.cu)."""
+    return max(1, min(8, 512 // ((columns + 31) // 32 * 32)))
+
+
+def _scan_smem(dim: int, vdim: int, staged_per_token: int) -> int:
+    """Bytes of shared memory of a scan kernel's block: sixteen staged tokens, and the state
+    unless a thread's share of a column (at most 64 rows) lies in registers."""
+    columns = max(dim, vdim)
+    if columns > 512:
+        return 1 << 30
+    rows = -(-dim // _scan_parts(columns))
+    state = 0 if rows <= 64 else dim * vdim + 4
+    return 4 * (state + 16 * staged_per_token + 256)
+
+
 def _f32(t: torch.Tensor) -> torch.Tensor:
     return t.to(torch.float32).contiguous()
 
@@ -47,9 +64,9 @@ class WkvMixer(Part):
         self.rank = int(p.get("decay_rank") or -1)
         self.names = {k: prefix + v for k, v in p["names"].items()}
         self.width = self.nh * self.dim
-        if (self.dim * self.dim + 4 + 7 * 16 * self.dim) * 4 > 200 * 1024:
+        if _scan_smem(self.dim, self.dim, (6 + _scan_parts(self.dim)) * self.dim) > 200 * 1024:
             raise ConfigError(f"a decaying state of {self.dim} x {self.dim} values per head is "
-                              "more than the kernel keeps in shared memory")
+                              "more than the kernel keeps on one multiprocessor")
 
     def libraries(self, rt) -> List[str]:
         return ["recurrent"]
@@ -69,27 +86,36 @@ class WkvMixer(Part):
     def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
         self.rt = rt
         n = self.names
-        self.mu = torch.stack([_f32(weights[n["mu_" + s]]) for s in self.MIXES]).contiguous()
-        self.proj = [Linear(weights[n[s]], rt) for s in ("r", "k", "v", "g")]
-        self.w1, self.w2 = Linear(weights[n["w1"]], rt), Linear(weights[n["w2"]], rt)
+        # W_s (h + (h' - h) mu_s) = [W_s | W_s diag(mu_s)] [h ; h' - h]: the five projections
+        # (r, k, v, g and the decay's first, low-rank one) are one product over rows of 2 W
+        ws = [weights[n[s]] for s in ("r", "k", "v", "g", "w1")]
+        kind = ws[0].dtype if len({w.dtype for w in ws}) == 1 else torch.float32
+        rows = []
+        for s, w in zip(self.MIXES, ws):
+            mu = _f32(weights[n["mu_" + s]])
+            rows.append(torch.cat([w.to(kind), (w.float() * mu[None, :]).to(kind)], dim=1))
+        self.fused = Linear(torch.cat(rows, dim=0), rt)
+        self.low_rank = ws[4].shape[0]
+        self.w2 = Linear(weights[n["w2"]], rt)
         self.w0, self.u = _f32(weights[n["w0"]]), _f32(weights[n["u"]]).reshape(-1)
         self.norm = _f32(weights[n["norm"]])
         self.o = Linear(weights[n["o"]], rt)
 
     def forward(self, h, x, step, line, state, writes_cache: bool, store: bool = False):
         T, dev, dt = h.shape[0], h.device, self.rt.dtype
-        mixes = torch.empty((5, T, self.hidden), dtype=dt, device=dev)
-        K.token_shift(h, state, step, self.mu, mixes)
-        z = torch.empty((5, T, self.width), dtype=torch.float32, device=dev)   # r, k, v, g, lw
-        for i, lin in enumerate(self.proj):
-            lin(mixes[i], out=z[i])
-        low = self.w1(mixes[4], out_dtype=torch.float32)
-        low_act = torch.empty(low.shape, dtype=dt, device=dev)
-        K.tanh_rows(low, low_act)
-        self.w2(low_act, out=z[4])
-        y = torch.empty((T, self.width), dtype=dt, device=dev)
-        K.wkv_scan(z[0], z[1], z[2], z[4], z[3], self.w0, self.u, self.norm, self.eps, state, h,
-                   step, y, self.nh, self.dim)
+        HD, R = self.width, self.low_rank
+        pair = torch.empty((T, 2 * self.hidden), dtype=dt, device=dev)
+        K.token_shift(h, state, step, pair)
+        # one row per token: r, k, v, g, the low-rank values, then the decay's logarithm
+        z = torch.empty((T, 5 * HD + R), dtype=torch.float32, device=dev)
+        self.fused(pair, out=z[:, :4 * HD + R])
+        low = torch.empty((T, R), dtype=dt, device=dev)
+        K.tanh_rows(z[:, 4 * HD:4 * HD + R], low)
+        self.w2(low, out=z[:, 4 * HD + R:])
+        y = torch.empty((T, HD), dtype=dt, device=dev)
+        K.wkv_scan(z[:, :HD], z[:, HD:2 * HD], z[:, 2 * HD:3 * HD], z[:, 4 * HD + R:],
+                   z[:, 3 * HD:4 * HD], self.w0, self.u, self.norm, self.eps, state, h, step, y,
+                   self.nh, self.dim)
         if store:
             self.o(y, out=x)
         else:
@@ -110,9 +136,10 @@ class MlstmMixer(Part):
         if self.cap <= 0:
             raise ConfigError(f"a gate cap of {self.cap}")
         self.names = {k: prefix + v for k, v in p["names"].items()}
-        if (self.dim * self.vdim + 4 + 16 * (3 * self.dim + 3 * self.vdim + 4)) * 4 > 200 * 1024:
+        staged = 3 * self.dim + (2 + _scan_parts(max(self.dim, self.vdim))) * self.vdim + 4
+        if _scan_smem(self.dim, self.vdim, staged) > 200 * 1024:
             raise ConfigError(f"a matrix memory of {self.dim} x {self.vdim} values per head is "
-                              "more than the kernel keeps in shared memory")
+                              "more than the kernel keeps on one multiprocessor")
 
     def libraries(self, rt) -> List[str]:
         return ["recurrent"]

@@ -201,7 +201,7 @@ class Routing:
     computation in 16 bits may fall on either side of such a call); where the margin is larger
     the difference is an error."""
 
-    def __init__(self, forced=None, close: float = 0.08):
+    def __init__(self, forced=None, close: float = 0.12):
         self.forced = forced or {}
         self.close = close
         self.margins: Dict = {}
