@@ -582,6 +582,44 @@ def test_long_decoding_from_the_first_token(small_u, dtype):
     eng.rt.check()
 
 
+def test_other_orders_of_layers(tmp_path):
+    """A model of decaying-state layers only (no keys and values anywhere: the cache has no
+    page pool at all) and one of parallel layers only, the second without feed-forwards; a
+    layer that uses the weights of a later one."""
+    from mormot2_ai_b200 import FimudraConfig, write_random_model
+    from tests.plain.qwen3_plain import read_safetensors
+    import json
+    moe = {"kind": "moe", "expert": {"ff": 24, "limit": 1.1},
+           "router": {"experts": 3, "top": 2, "identity": 1, "scale": 0.8}}
+    wkv = {"type": "wkv", "mixer": {"heads": 2, "dim": 16, "decay_rank": 4}, "mlp": moe}
+    par = {"type": "parallel", "mlp": None, "mixer": {
+        "left": {"heads": 2, "kv_heads": 2, "dim": 32, "vdim": 16, "scale": 0.2,
+                 "rot": {"base": 100.0, "dims": 32}},
+        "right": {"heads": 2, "dim": 16, "vdim": 32, "gate_cap": 5.0},
+        "left_scale": 0.5, "right_scale": 0.5}}
+    docs = [{"architecture": "Fimudra", "vocab": 97, "width": 40, "norm": {"eps": 1e-5},
+             "embedding": {"scale": 2.0}, "streams": 2, "layers": [dict(wkv, weights_of=1), wkv, wkv]},
+            {"architecture": "Fimudra", "vocab": 61, "width": 48, "norm": {"eps": 1e-6},
+             "streams": 4, "layers": [par, dict(par, weights_of=0)]}]
+    for k, doc in enumerate(docs):
+        folder = str(tmp_path / f"m{k}")
+        write_random_model(folder, FimudraConfig.from_dict(doc), 40 + k, std=0.1, norm_std=0.2)
+        W = {n: np.asarray(v, dtype=np.float64)
+             for n, v in read_safetensors(folder + "/model.safetensors").items()}
+        with open(folder + "/config.json") as f:
+            cfg = json.load(f)
+        ids = np.random.default_rng(k).integers(0, doc["vocab"], 90).tolist()
+        ref = plain.forward(cfg, W, ids)
+        eng = Engine.from_folder(folder, dtype="float32", max_tokens=256)
+        assert len(eng.plans) == (0 if k == 0 else 1)
+        slot = eng.open()
+        got = [eng.step([Entry(slot, ids[:70], list(range(70)))]).cpu().numpy()]
+        got += [eng.step([Entry(slot, [t])]).cpu().numpy().copy() for t in ids[70:]]
+        eng.close(slot)
+        check(np.concatenate(got), ref, "float32", f"order {k}")
+        eng.rt.check()
+
+
 def test_a_step_that_fails_leaves_the_state_as_it_found_it(small_u):
     """A refused step changes nothing, and after it the sequence goes on as if it had not been."""
     small = small_u
