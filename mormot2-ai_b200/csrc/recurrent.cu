@@ -57,73 +57,81 @@ MB_EXPORT int mb_token_shift(const void* h, int dtype, const float* state, long 
   MB_CHECK_LAUNCH("mb_token_shift");
 }
 
-// ------------------------------------------------------------------ decaying matrix state
-// A block stages SCAN_CT tokens of its head's inputs in shared memory at once (all loads in
-// flight together), walks them without a barrier between tokens (a thread reads the staged
-// vectors and its own column of the state), and then norms the chunk's outputs a warp a token.
+// ------------------------------------------------------------------ the walks over the tokens
+// A block owns a slice of a head's value columns (all of them where the batch gives blocks
+// enough; else the columns are dealt over several blocks so that a single prompt does not
+// leave most multiprocessors idle, and the heads' unit norm runs as a kernel after). It
+// stages SCAN_CT tokens of its head's inputs in shared memory at once (all loads in flight
+// together) and walks them without a barrier between tokens: P groups of threads share the
+// rows of a column, a thread keeps its rows of its column in registers (R of them at most;
+// R = 0: more than 32, the state then lies in shared memory) and reads the staged vectors.
 #define SCAN_CT 16
 
+__device__ __forceinline__ int pad32(int v) { return (v + 31) & ~31; }
+
 // r, k, v, lw, g: float32 [T, ld] each (head hd's values at column hd * D + i); w0, u, normw:
-// float32 [H * D]. State of a slot: [W values of the last h | H x D x D]. out [T, H * D].
-// R > 0: a thread keeps its share of a state column (R rows at most) in registers, and shared
-// memory only carries the staged tokens; R = 0: the state lies in shared memory (heads too
-// large for the registers of 512 threads).
+// float32 [H * D]. State of a slot: [W values of the last h | H x D x D]. out [T, H * D] (one
+// slice of columns a head: normed and gated here); raw [T, H * D] float32 (several slices: the
+// outputs as they are, for head_norm_gate_kernel).
 template <typename T, int R>
-__global__ void __launch_bounds__(512) wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ k,
-                                const float* __restrict__ v, const float* __restrict__ lw,
-                                const float* __restrict__ g, int ld,
-                                const float* __restrict__ w0, const float* __restrict__ u,
-                                const float* __restrict__ normw, float eps,
-                                float* __restrict__ state, size_t state_stride, size_t state_off,
-                                const T* __restrict__ h, int W, const int* __restrict__ seq_start,
-                                const int* __restrict__ seq_slot, T* __restrict__ out, int H,
-                                int D) {
+__global__ void __launch_bounds__(512, 1)
+wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ k,
+                const float* __restrict__ v, const float* __restrict__ lw,
+                const float* __restrict__ g, int ld, const float* __restrict__ w0,
+                const float* __restrict__ u, const float* __restrict__ normw, float eps,
+                float* __restrict__ state, size_t state_stride, size_t state_off,
+                const T* __restrict__ h, int W, const int* __restrict__ seq_start,
+                const int* __restrict__ seq_slot, T* __restrict__ out, float* __restrict__ raw,
+                int H, int D) {
   mb_grid_wait();
   mb_grid_launch_next();
   extern __shared__ __align__(16) float wk_smem[];
-  const int DD = (D * D + 3) & ~3;
-  float* S = wk_smem;                        // [D][D], S[i * D + j]: key channel i, value channel j
-  float4* vec = (float4*)(S + (R > 0 ? 0 : DD));   // [CT][D]: r, k, decay, u * k
-  float* sv = (float*)(vec + SCAN_CT * D + 64);   // [CT][D] v (64 entries of room behind vec:
-                                                  // a thread may read past its last row)
-  float* sg = sv + SCAN_CT * D;              // [CT][D] g
-  float* so = sg + SCAN_CT * D;              // [CT][P][D] o, the sums over each part's channels
+  const int NS = gridDim.z, CW = (D + NS - 1) / NS;
+  const int c0 = blockIdx.z * CW, cw = max(0, min(D, c0 + CW) - c0);
+  const int Cp = pad32(CW), P = blockDim.x / Cp;
+  const int part = threadIdx.x / Cp, j = threadIdx.x - part * Cp;
+  const int per = (D + P - 1) / P, i0 = min(D, part * per), cnt = min(D, i0 + per) - i0;
+  float* S = wk_smem;                                  // [D][CW] (R = 0 only)
+  float4* vec = (float4*)(S + (R > 0 ? 0 : ((D * CW + 3) & ~3)));   // [CT][D]: r, k, decay, u k
+  float* sv = (float*)(vec + SCAN_CT * D + 64);        // [CT][CW] v (64 entries of room behind
+                                                       // vec: a thread may read past its rows)
+  float* sg = sv + SCAN_CT * CW;                       // [CT][CW] g
+  float* so = sg + SCAN_CT * CW;                       // [CT][P][CW] o, summed over a part's rows
   const int b = blockIdx.x, hd = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  // P groups of threads share the key channels of a column: thread (part, j) owns rows
-  // i0 .. i1 of column j of the state
-  const int Dp = (D + 31) & ~31, P = blockDim.x / Dp;
-  const int part = threadIdx.x / Dp, j = threadIdx.x - part * Dp;
-  const int per = (D + P - 1) / P, i0 = min(D, part * per), i1 = min(D, i0 + per);
-  const int cnt = i1 - i0;
   const int t0 = seq_start[b], n = seq_start[b + 1] - t0;
   float* st = state + (size_t)seq_slot[b] * state_stride + state_off;
-  float* Sg = st + W + (size_t)hd * D * D;
-  const bool own = j < D;
+  float* Sg = st + W + (size_t)hd * D * D + c0;        // row i of this slice at Sg + i * D
+  const bool own = j < cw && part < P;
   float Sr[R > 0 ? R : 1];
   if (R > 0) {
 #pragma unroll
-    for (int q = 0; q < (R > 0 ? R : 1); ++q) Sr[q] = (own && i0 + q < i1) ? Sg[(i0 + q) * D + j] : 0.f;
+    for (int q = 0; q < (R > 0 ? R : 1); ++q)
+      Sr[q] = (own && q < cnt) ? Sg[(size_t)(i0 + q) * D + j] : 0.f;
   } else {
-    for (int e = threadIdx.x; e < D * D; e += blockDim.x) S[e] = Sg[e];
+    for (int e = threadIdx.x; e < D * cw; e += blockDim.x) {
+      const int i = e / cw, jj = e - i * cw;
+      S[i * CW + jj] = Sg[(size_t)i * D + jj];
+    }
   }
-  const int col = hd * D + j;
-  const float w0j = own ? w0[col] : 0.f, uj = own ? u[col] : 0.f;
-  for (int c0 = 0; c0 < n; c0 += SCAN_CT) {
-    const int cn = min(SCAN_CT, n - c0);
-    if (own) {
-      for (int tt = part; tt < cn; tt += P) {
-        const size_t at = (size_t)(t0 + c0 + tt) * ld + col;
-        const float kj = k[at];
-        vec[tt * D + j] = make_float4(r[at], kj, expf(-expf(lw[at] + w0j)), uj * kj);
-        sv[tt * D + j] = v[at];
-        sg[tt * D + j] = g[at];
-      }
+  for (int c = 0; c < n; c += SCAN_CT) {
+    const int cn = min(SCAN_CT, n - c);
+    for (int e = threadIdx.x; e < cn * D; e += blockDim.x) {
+      const int tt = e / D, i = e - tt * D;
+      const size_t at = (size_t)(t0 + c + tt) * ld + hd * D + i;
+      const float kk = k[at];
+      vec[e] = make_float4(r[at], kk, expf(-expf(lw[at] + w0[hd * D + i])), u[hd * D + i] * kk);
+    }
+    for (int e = threadIdx.x; e < cn * cw; e += blockDim.x) {
+      const int tt = e / cw, jj = e - tt * cw;
+      const size_t at = (size_t)(t0 + c + tt) * ld + hd * D + c0 + jj;
+      sv[tt * CW + jj] = v[at];
+      sg[tt * CW + jj] = g[at];
     }
     __syncthreads();
     if (own) {
       for (int tt = 0; tt < cn; ++tt) {
-        const float vj = sv[tt * D + j];
+        const float vj = sv[tt * CW + j];
         const float4* x = vec + tt * D;
         float o = 0.f;
         if (R > 0) {
@@ -141,48 +149,58 @@ __global__ void __launch_bounds__(512) wkv_scan_kernel(const float* __restrict__
         } else {
           // eight rows at a time: their loads are asked for together, then the multiply-adds,
           // then the stores (written one by one a store would hold the next load back)
-          for (int ib = i0; ib < i1; ib += 8) {
+          for (int ib = i0; ib < i0 + cnt; ib += 8) {
             float4 xi[8];
             float sc[8];
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-              const int i = min(ib + q, i1 - 1);
+              const int i = min(ib + q, i0 + cnt - 1);
               xi[q] = x[i];
-              sc[q] = S[i * D + j];
+              sc[q] = S[i * CW + j];
             }
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-              if (ib + q < i1) {
+              if (ib + q < i0 + cnt) {
                 o = fmaf(xi[q].x, fmaf(xi[q].w, vj, sc[q]), o);
-                S[(ib + q) * D + j] = fmaf(xi[q].z, sc[q], xi[q].y * vj);
+                S[(ib + q) * CW + j] = fmaf(xi[q].z, sc[q], xi[q].y * vj);
               }
             }
           }
         }
-        so[(tt * P + part) * D + j] = o;
+        so[(tt * P + part) * CW + j] = o;
       }
     }
     __syncthreads();
-    for (int tt = warp; tt < cn; tt += warps) {
-      float ov[8];     // heads of up to 256 values a lane's eight; beyond, the sums are formed again
-      float ss = 0.f;
-      for (int i = lane, q = 0; i < D; i += 32, ++q) {
+    if (raw != nullptr) {
+      for (int e = threadIdx.x; e < cn * cw; e += blockDim.x) {
+        const int tt = e / cw, jj = e - tt * cw;
         float o = 0.f;
-        for (int pp = 0; pp < P; ++pp) o += so[(tt * P + pp) * D + i];
-        if (q < 8) ov[q] = o;
-        ss = fmaf(o, o, ss);
+        for (int pp = 0; pp < P; ++pp) o += so[(tt * P + pp) * CW + jj];
+        raw[(size_t)(t0 + c + tt) * H * D + hd * D + c0 + jj] = o;
       }
-      const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
-      T* orow = out + (size_t)(t0 + c0 + tt) * H * D + hd * D;
-      for (int i = lane, q = 0; i < D; i += 32, ++q) {
-        float o = 0.f;
-        if (q < 8) {
-          o = ov[q];
-        } else {
-          for (int pp = 0; pp < P; ++pp) o += so[(tt * P + pp) * D + i];
+    } else {
+      // one slice: the head's unit norm, its weight and the gate here, a warp a token
+      for (int tt = warp; tt < cn; tt += warps) {
+        float ov[8];   // heads of up to 256 values a lane's eight; beyond, the sums are formed again
+        float ss = 0.f;
+        for (int i = lane, q = 0; i < D; i += 32, ++q) {
+          float o = 0.f;
+          for (int pp = 0; pp < P; ++pp) o += so[(tt * P + pp) * CW + i];
+          if (q < 8) ov[q] = o;
+          ss = fmaf(o, o, ss);
         }
-        const float gi = sg[tt * D + i];
-        orow[i] = from_f32<T>(o * inv * normw[hd * D + i] * (gi / (1.0f + expf(-gi))));
+        const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
+        T* orow = out + (size_t)(t0 + c + tt) * H * D + hd * D;
+        for (int i = lane, q = 0; i < D; i += 32, ++q) {
+          float o = 0.f;
+          if (q < 8) {
+            o = ov[q];
+          } else {
+            for (int pp = 0; pp < P; ++pp) o += so[(tt * P + pp) * CW + i];
+          }
+          const float gi = sg[tt * CW + i];
+          orow[i] = from_f32<T>(o * inv * normw[hd * D + i] * (gi / (1.0f + expf(-gi))));
+        }
       }
     }
     __syncthreads();
@@ -190,67 +208,121 @@ __global__ void __launch_bounds__(512) wkv_scan_kernel(const float* __restrict__
   if (R > 0) {
 #pragma unroll
     for (int q = 0; q < (R > 0 ? R : 1); ++q)
-      if (own && i0 + q < i1) Sg[(i0 + q) * D + j] = Sr[q];
+      if (own && q < cnt) Sg[(size_t)(i0 + q) * D + j] = Sr[q];
   } else {
-    for (int e = threadIdx.x; e < D * D; e += blockDim.x) Sg[e] = S[e];
+    for (int e = threadIdx.x; e < D * cw; e += blockDim.x) {
+      const int i = e / cw, jj = e - i * cw;
+      Sg[(size_t)i * D + jj] = S[i * CW + jj];
+    }
   }
-  if (hd == 0 && n > 0)
-    for (int c = threadIdx.x; c < W; c += blockDim.x)
-      st[c] = to_f32<T>(h[(size_t)(t0 + n - 1) * W + c]);
+  if (hd == 0 && blockIdx.z == 0 && n > 0)
+    for (int cc = threadIdx.x; cc < W; cc += blockDim.x)
+      st[cc] = to_f32<T>(h[(size_t)(t0 + n - 1) * W + cc]);
 }
 
-// how many groups of threads share a column's key channels: as many as keep a block within
-// 512 threads, at most 8
+// out[t, hd, :] = o / rms(o) * normw * gate(g) for every token and head, a warp each; o: raw
+// [T, H * DV] float32; g: the gates' logits, head hd of token t at g + t * ldg + hd * DV;
+// gate 0: g sigmoid(g), 1: sigmoid(g).
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* __restrict__ raw, const float* __restrict__ g,
+                                      int ldg, const float* __restrict__ normw, float eps,
+                                      int gate, T* __restrict__ out, int rows, int H, int DV) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (idx >= rows) return;
+  const int t = idx / H, hd = idx - t * H;
+  const float* o = raw + (size_t)idx * DV;
+  const float* gg = g + (size_t)t * ldg + hd * DV;
+  float ss = 0.f;
+  for (int i = lane; i < DV; i += 32) ss = fmaf(o[i], o[i], ss);
+  const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)DV + eps);
+  for (int i = lane; i < DV; i += 32) {
+    const float gi = gg[i], sig = 1.0f / (1.0f + expf(-gi));
+    out[(size_t)idx * DV + i] = from_f32<T>(o[i] * inv * normw[hd * DV + i] * (gate ? sig : gi * sig));
+  }
+}
+
+template <typename T>
+static void launch_head_norm(const float* raw, const float* g, int ldg, const float* normw,
+                             float eps, int gate, void* out, int T_, int H, int DV,
+                             cudaStream_t s) {
+  const int rows = T_ * H;
+  mb_launch(head_norm_gate_kernel<T>, dim3((rows + 3) / 4), dim3(128), 0, s, raw, g, ldg, normw,
+            eps, gate, (T*)out, rows, H, DV);
+}
+
+// how many groups of threads share a column's rows: as many as keep a block within 512
+// threads, at most 8
 static int scan_parts(int columns) {
   const int cp = (columns + 31) / 32 * 32;
   int p = 512 / cp;
   return p < 1 ? 1 : (p > 8 ? 8 : p);
 }
 
-// the rows of a state column that one thread has: 8, 16, 32 or 64 in registers, 0: more, the
+// the rows of a state column that one thread has: 8, 16 or 32 in registers, 0: more, the
 // state stays in shared memory
 static int scan_rows(int D, int columns) {
   const int P = scan_parts(columns), per = (D + P - 1) / P;
-  return per <= 8 ? 8 : per <= 16 ? 16 : per <= 32 ? 32 : per <= 64 ? 64 : 0;
+  return per <= 8 ? 8 : per <= 16 ? 16 : per <= 32 ? 32 : 0;
 }
 
-static size_t wkv_smem_bytes(int D) {
-  const size_t state = scan_rows(D, D) ? 0 : (size_t)((D * D + 3) & ~3);
-  return (state + (size_t)SCAN_CT * D * (6 + scan_parts(D)) + 64 * 4) * sizeof(float);
+// Over how many blocks a head's DV value columns (of D rows) are dealt: one while the step has
+// 96 (sequence, head) pairs or more (a decode step of a batch), else doubled while a slice
+// holds more than 4,096 values of the state (measured: below that a block's time is the
+// chunks' fixed cost, and more blocks gain nothing), keeps 32 columns and the block
+// `need_threads` threads. It depends on the step's shape only.
+static int scan_slices(int B, int H, int D, int DV, int need_threads) {
+  int ns = 1;
+  while (B * H * ns < 96 && D * ((DV + ns - 1) / ns) > 4096) {
+    const int cw = (DV + 2 * ns - 1) / (2 * ns);
+    if (cw < 32 || ((cw + 31) / 32 * 32) * scan_parts(cw) < need_threads) break;
+    ns *= 2;
+  }
+  return ns;
 }
 
+static size_t wkv_smem_bytes(int D, int CW) {
+  const size_t state = scan_rows(D, CW) ? 0 : (size_t)((D * CW + 3) & ~3);
+  return (state + (size_t)SCAN_CT * (4 * D + CW * (2 + scan_parts(CW))) + 64 * 4) * sizeof(float);
+}
+
+// `raw`: float32 [T, H * D] of scratch, used when a head's columns are dealt over several blocks.
 MB_EXPORT int mb_wkv_scan(const float* r, const float* k, const float* v, const float* lw,
                           const float* g, int ld, const float* w0, const float* u,
                           const float* normw, float eps, float* state, long long state_stride,
                           long long state_off, const void* h, int dtype, int W,
-                          const int* seq_start, const int* seq_slot, void* out, int B, int H,
-                          int D, void* stream) {
+                          const int* seq_start, const int* seq_slot, void* out, float* raw,
+                          int T_, int B, int H, int D, void* stream) {
   if (B <= 0) return 0;
-  const size_t smem = wkv_smem_bytes(D);
-  if (D <= 0 || D > 512 || smem > 200 * 1024)
-    MB_FAIL("mb_wkv_scan: heads of %d values (at most 512, and what a block stages must fit "
-            "200 KB)", D);
+  if (D <= 0 || D > 512) MB_FAIL("mb_wkv_scan: heads of %d values (at most 512)", D);
+  const int NS = raw ? scan_slices(B, H, D, D, 32) : 1;
+  const int CW = (D + NS - 1) / NS;
+  const size_t smem = wkv_smem_bytes(D, CW);
+  if (smem > 200 * 1024)
+    MB_FAIL("mb_wkv_scan: heads of %d values (what a block stages must fit 200 KB)", D);
   cudaStream_t s = (cudaStream_t)stream;
-  const int threads = (D + 31) / 32 * 32 * scan_parts(D);
-#define GO(T_, R_)                                                                             \
+  const int threads = (CW + 31) / 32 * 32 * scan_parts(CW);
+  float* raw_used = NS > 1 ? raw : nullptr;
+#define GO(T_t, R_)                                                                            \
   {                                                                                            \
     static size_t configured = 48 * 1024;                                                      \
     if (smem > configured) {                                                                   \
-      cudaFuncSetAttribute(wkv_scan_kernel<T_, R_>,                                            \
+      cudaFuncSetAttribute(wkv_scan_kernel<T_t, R_>,                                           \
                            cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);           \
       configured = 200 * 1024;                                                                 \
     }                                                                                          \
-    mb_launch(wkv_scan_kernel<T_, R_>, dim3(B, H), dim3(threads), smem, s, r, k, v, lw, g, ld, \
-              w0, u, normw, eps, state, (size_t)state_stride, (size_t)state_off, (const T_*)h, \
-              W, seq_start, seq_slot, (T_*)out, H, D);                                         \
+    mb_launch(wkv_scan_kernel<T_t, R_>, dim3(B, H, NS), dim3(threads), smem, s, r, k, v, lw, g, \
+              ld, w0, u, normw, eps, state, (size_t)state_stride, (size_t)state_off,           \
+              (const T_t*)h, W, seq_start, seq_slot, (T_t*)out, raw_used, H, D);               \
+    if (NS > 1) launch_head_norm<T_t>(raw, g, ld, normw, eps, 0, out, T_, H, D, s);            \
   }
-#define GOR(T_)                                                                                \
-  switch (scan_rows(D, D)) {                                                                   \
-    case 8: GO(T_, 8) break;                                                                   \
-    case 16: GO(T_, 16) break;                                                                 \
-    case 32: GO(T_, 32) break;                                                                 \
-    case 64: GO(T_, 64) break;                                                                 \
-    default: GO(T_, 0)                                                                         \
+#define GOR(T_t)                                                                               \
+  switch (scan_rows(D, CW)) {                                                                  \
+    case 8: GO(T_t, 8) break;                                                                  \
+    case 16: GO(T_t, 16) break;                                                                \
+    case 32: GO(T_t, 32) break;                                                                \
+    default: GO(T_t, 0)                                                                        \
   }
   if (dtype == MB_F32) GOR(float) else GOR(__nv_bfloat16)
 #undef GOR
@@ -262,62 +334,71 @@ MB_EXPORT int mb_wkv_scan(const float* r, const float* k, const float* v, const 
 // z: float32 [T, ld], the fused projection: q at column cq + hd * D, k at ck + hd * D, v at
 // cv + hd * DV, the output gate at cg + hd * DV, the input and forget gates at ci + hd and
 // cf + hd. bi, bf: float32 [H]. normw: float32 [H * DV]. State of a slot, per head:
-// [D x DV | D of n | m].
+// [D x DV | D of n | m]. out / raw as in wkv_scan_kernel (raw holds S^T q over its denominator).
 __device__ __forceinline__ float log_sigmoid(float x) {
   return fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
 }
 
 template <typename T, int R>
-__global__ void __launch_bounds__(512) mlstm_scan_kernel(const float* __restrict__ z, int ld, int cq, int ck, int cv,
-                                  int cg, int ci, int cf, const float* __restrict__ bi,
-                                  const float* __restrict__ bf, float cap, float q_scale,
-                                  const float* __restrict__ normw, float eps,
-                                  float* __restrict__ state, size_t state_stride,
-                                  size_t state_off, const int* __restrict__ seq_start,
-                                  const int* __restrict__ seq_slot, T* __restrict__ out, int H,
-                                  int D, int DV) {
+__global__ void __launch_bounds__(512, 1)
+mlstm_scan_kernel(const float* __restrict__ z, int ld, int cq, int ck, int cv, int cg, int ci,
+                  int cf, const float* __restrict__ bi, const float* __restrict__ bf, float cap,
+                  float q_scale, const float* __restrict__ normw, float eps,
+                  float* __restrict__ state, size_t state_stride, size_t state_off,
+                  const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                  T* __restrict__ out, float* __restrict__ raw, int H, int D, int DV) {
   mb_grid_wait();
   mb_grid_launch_next();
   extern __shared__ __align__(16) float ml_smem[];
-  const int DD = (D * DV + 3) & ~3;
-  float* S = ml_smem;                          // [D][DV]
-  float2* qk = (float2*)(S + (R > 0 ? 0 : DD));   // [CT][D]: q (scaled), k
-  float* sv = (float*)(qk + SCAN_CT * D + 64); // [CT][DV] v (64 entries of room behind qk)
-  float* sg = sv + SCAN_CT * DV;               // [CT][DV] the output gate's logit
-  float* snq = sg + SCAN_CT * DV;              // [CT][D] n_i q_i
-  float* sab = snq + SCAN_CT * D;              // [CT][4]: the state's factor, the input's, e^(-m)
-  float* snum = sab + SCAN_CT * 4;             // [CT][P][DV] S^T q, summed over each part's rows
+  const int NS = gridDim.z, CW = (DV + NS - 1) / NS;
+  const int c0 = blockIdx.z * CW, cw = max(0, min(DV, c0 + CW) - c0);
+  // one slice: the block is as wide as the larger of D and DV (a thread a normalizer value)
+  const int Cp = NS == 1 ? pad32(max(D, DV)) : pad32(CW), P = blockDim.x / Cp;
+  const int part = threadIdx.x / Cp, j = threadIdx.x - part * Cp;
+  const int per = (D + P - 1) / P, i0 = min(D, part * per), cnt = min(D, i0 + per) - i0;
+  float* S = ml_smem;                                   // [D][CW] (R = 0 only)
+  float2* qk = (float2*)(S + (R > 0 ? 0 : ((D * CW + 3) & ~3)));   // [CT][D]: q (scaled), k
+  float* sv = (float*)(qk + SCAN_CT * D + 64);          // [CT][CW] v (64 entries of room behind qk)
+  float* sg = sv + SCAN_CT * CW;                        // [CT][CW] the output gate's logit
+  float* snq = sg + SCAN_CT * CW;                       // [CT][D] n_i q_i
+  float* sab = snq + SCAN_CT * D;                       // [CT][4]: the state's factor, the
+                                                        // input's, e^(-m), the denominator
+  float* snum = sab + SCAN_CT * 4;                      // [CT][P][CW] S^T q, summed over a part's rows
   const int b = blockIdx.x, hd = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  // P groups of threads share the key channels of a column, as in wkv_scan_kernel
-  const int Cp = ((D > DV ? D : DV) + 31) & ~31, P = blockDim.x / Cp;
-  const int part = threadIdx.x / Cp, j = threadIdx.x - part * Cp;
-  const int per = (D + P - 1) / P, i0 = min(D, part * per), i1 = min(D, i0 + per);
-  const int cnt = i1 - i0;
   const int t0 = seq_start[b], n = seq_start[b + 1] - t0;
   float* st = state + (size_t)seq_slot[b] * state_stride + state_off +
               (size_t)hd * ((size_t)D * DV + D + 1);
-  const bool own_k = j < D && part == 0, own_v = j < DV;
+  float* Sg = st + c0;                                  // row i of this slice at Sg + i * DV
+  const bool own_v = j < cw && part < P, own_k = (int)threadIdx.x < D;
   float Sr[R > 0 ? R : 1];
   if (R > 0) {
 #pragma unroll
     for (int q = 0; q < (R > 0 ? R : 1); ++q)
-      Sr[q] = (own_v && i0 + q < i1) ? st[(size_t)(i0 + q) * DV + j] : 0.f;
+      Sr[q] = (own_v && q < cnt) ? Sg[(size_t)(i0 + q) * DV + j] : 0.f;
   } else {
-    for (int e = threadIdx.x; e < D * DV; e += blockDim.x) S[e] = st[e];
+    for (int e = threadIdx.x; e < D * cw; e += blockDim.x) {
+      const int i = e / cw, jj = e - i * cw;
+      S[i * CW + jj] = Sg[(size_t)i * DV + jj];
+    }
   }
-  float nj = own_k ? st[(size_t)D * DV + j] : 0.f;
+  // every slice keeps the whole normalizer and the running maximum (they need all of k); the
+  // first one writes them back
+  float nj = own_k ? st[(size_t)D * DV + threadIdx.x] : 0.f;
   float m = st[(size_t)D * DV + D];          // the last thread's copy is the one that counts
   const float bih = bi[hd], bfh = bf[hd];
-  for (int c0 = 0; c0 < n; c0 += SCAN_CT) {
-    const int cn = min(SCAN_CT, n - c0);
-    for (int tt = part; tt < cn; tt += P) {
-      const float* zr = z + (size_t)(t0 + c0 + tt) * ld;
-      if (j < D) qk[tt * D + j] = make_float2(zr[cq + hd * D + j] * q_scale, zr[ck + hd * D + j]);
-      if (own_v) {
-        sv[tt * DV + j] = zr[cv + hd * DV + j];
-        sg[tt * DV + j] = zr[cg + hd * DV + j];
-      }
+  for (int c = 0; c < n; c += SCAN_CT) {
+    const int cn = min(SCAN_CT, n - c);
+    for (int e = threadIdx.x; e < cn * D; e += blockDim.x) {
+      const int tt = e / D, i = e - tt * D;
+      const float* zr = z + (size_t)(t0 + c + tt) * ld;
+      qk[e] = make_float2(zr[cq + hd * D + i] * q_scale, zr[ck + hd * D + i]);
+    }
+    for (int e = threadIdx.x; e < cn * cw; e += blockDim.x) {
+      const int tt = e / cw, jj = e - tt * cw;
+      const float* zr = z + (size_t)(t0 + c + tt) * ld;
+      sv[tt * CW + jj] = zr[cv + hd * DV + c0 + jj];
+      sg[tt * CW + jj] = zr[cg + hd * DV + c0 + jj];
     }
     if (warp == warps - 1) {
       // the gates by the last warp: every token's two logarithms side by side (a lane a
@@ -325,7 +406,7 @@ __global__ void __launch_bounds__(512) mlstm_scan_kernel(const float* __restrict
       // only), then the exponentials side by side again
       float gi = 0.f, gf = 0.f;
       if (lane < cn) {
-        const float* zr = z + (size_t)(t0 + c0 + lane) * ld;
+        const float* zr = z + (size_t)(t0 + c + lane) * ld;
         gi = cap * tanhf((zr[ci + hd] + bih) / cap);
         gf = log_sigmoid(cap * tanhf((zr[cf + hd] + bfh) / cap));
         sab[lane * 4] = gi;
@@ -352,12 +433,12 @@ __global__ void __launch_bounds__(512) mlstm_scan_kernel(const float* __restrict
     for (int tt = 0; tt < cn; ++tt) {
       const float a = sab[tt * 4], bb = sab[tt * 4 + 1];
       if (own_k) {
-        const float2 x = qk[tt * D + j];
+        const float2 x = qk[tt * D + threadIdx.x];
         nj = fmaf(a, nj, bb * x.y);
-        snq[tt * D + j] = nj * x.x;
+        snq[tt * D + threadIdx.x] = nj * x.x;
       }
       if (own_v) {
-        const float bv = bb * sv[tt * DV + j];
+        const float bv = bb * sv[tt * CW + j];
         const float2* x = qk + tt * D;
         float num = 0.f;
         if (R > 0) {
@@ -372,53 +453,69 @@ __global__ void __launch_bounds__(512) mlstm_scan_kernel(const float* __restrict
           }
           num = (n4[0] + n4[1]) + (n4[2] + n4[3]);
         } else {
-          for (int ib = i0; ib < i1; ib += 8) {     // eight rows at a time, as in wkv_scan_kernel
+          for (int ib = i0; ib < i0 + cnt; ib += 8) {   // eight rows at a time, as in wkv_scan_kernel
             float2 xi[8];
             float sc[8];
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-              const int i = min(ib + q, i1 - 1);
+              const int i = min(ib + q, i0 + cnt - 1);
               xi[q] = x[i];
-              sc[q] = S[i * DV + j];
+              sc[q] = S[i * CW + j];
             }
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-              if (ib + q < i1) {
+              if (ib + q < i0 + cnt) {
                 const float s = fmaf(a, sc[q], xi[q].y * bv);
-                S[(ib + q) * DV + j] = s;
+                S[(ib + q) * CW + j] = s;
                 num = fmaf(s, xi[q].x, num);
               }
             }
           }
         }
-        snum[(tt * P + part) * DV + j] = num;
+        snum[(tt * P + part) * CW + j] = num;
       }
     }
     __syncthreads();
-    for (int tt = warp; tt < cn; tt += warps) {
-      float nv[8];     // value rows of up to 256 a lane's eight; beyond, the sums are formed again
-      float nq = 0.f, ss = 0.f;
-      for (int i = lane; i < D; i += 32) nq += snq[tt * D + i];
-      for (int i = lane, q = 0; i < DV; i += 32, ++q) {
-        float num = 0.f;
-        for (int pp = 0; pp < P; ++pp) num += snum[(tt * P + pp) * DV + i];
-        if (q < 8) nv[q] = num;
-        ss = fmaf(num, num, ss);
+    if (raw != nullptr) {
+      for (int tt = warp; tt < cn; tt += warps) {
+        float nq = 0.f;
+        for (int i = lane; i < D; i += 32) nq += snq[tt * D + i];
+        nq = warp_sum(nq);
+        if (lane == 0) sab[tt * 4 + 3] = fmaxf(fabsf(nq), sab[tt * 4 + 2]) + 1e-6f;
       }
-      nq = warp_sum(nq);
-      ss = warp_sum(ss);
-      const float den = fmaxf(fabsf(nq), sab[tt * 4 + 2]) + 1e-6f;
-      const float inv = 1.0f / sqrtf(ss / (den * den) / (float)DV + eps);
-      T* orow = out + (size_t)(t0 + c0 + tt) * H * DV + hd * DV;
-      for (int i = lane, q = 0; i < DV; i += 32, ++q) {
+      __syncthreads();
+      for (int e = threadIdx.x; e < cn * cw; e += blockDim.x) {
+        const int tt = e / cw, jj = e - tt * cw;
         float num = 0.f;
-        if (q < 8) {
-          num = nv[q];
-        } else {
-          for (int pp = 0; pp < P; ++pp) num += snum[(tt * P + pp) * DV + i];
+        for (int pp = 0; pp < P; ++pp) num += snum[(tt * P + pp) * CW + jj];
+        raw[(size_t)(t0 + c + tt) * H * DV + hd * DV + c0 + jj] = num / sab[tt * 4 + 3];
+      }
+    } else {
+      for (int tt = warp; tt < cn; tt += warps) {
+        float nv[8];   // value rows of up to 256 a lane's eight; beyond, the sums are formed again
+        float nq = 0.f, ss = 0.f;
+        for (int i = lane; i < D; i += 32) nq += snq[tt * D + i];
+        for (int i = lane, q = 0; i < DV; i += 32, ++q) {
+          float num = 0.f;
+          for (int pp = 0; pp < P; ++pp) num += snum[(tt * P + pp) * CW + i];
+          if (q < 8) nv[q] = num;
+          ss = fmaf(num, num, ss);
         }
-        const float gate = 1.0f / (1.0f + expf(-sg[tt * DV + i]));
-        orow[i] = from_f32<T>(num / den * inv * normw[hd * DV + i] * gate);
+        nq = warp_sum(nq);
+        ss = warp_sum(ss);
+        const float den = fmaxf(fabsf(nq), sab[tt * 4 + 2]) + 1e-6f;
+        const float inv = 1.0f / sqrtf(ss / (den * den) / (float)DV + eps);
+        T* orow = out + (size_t)(t0 + c + tt) * H * DV + hd * DV;
+        for (int i = lane, q = 0; i < DV; i += 32, ++q) {
+          float num = 0.f;
+          if (q < 8) {
+            num = nv[q];
+          } else {
+            for (int pp = 0; pp < P; ++pp) num += snum[(tt * P + pp) * CW + i];
+          }
+          const float gate = 1.0f / (1.0f + expf(-sg[tt * CW + i]));
+          orow[i] = from_f32<T>(num / den * inv * normw[hd * DV + i] * gate);
+        }
       }
     }
     __syncthreads();
@@ -426,51 +523,65 @@ __global__ void __launch_bounds__(512) mlstm_scan_kernel(const float* __restrict
   if (R > 0) {
 #pragma unroll
     for (int q = 0; q < (R > 0 ? R : 1); ++q)
-      if (own_v && i0 + q < i1) st[(size_t)(i0 + q) * DV + j] = Sr[q];
+      if (own_v && q < cnt) Sg[(size_t)(i0 + q) * DV + j] = Sr[q];
   } else {
-    for (int e = threadIdx.x; e < D * DV; e += blockDim.x) st[e] = S[e];
+    for (int e = threadIdx.x; e < D * cw; e += blockDim.x) {
+      const int i = e / cw, jj = e - i * cw;
+      Sg[(size_t)i * DV + jj] = S[i * CW + jj];
+    }
   }
-  if (own_k) st[(size_t)D * DV + j] = nj;
-  if (threadIdx.x == blockDim.x - 1) st[(size_t)D * DV + D] = m;
+  if (blockIdx.z == 0) {
+    if (own_k) st[(size_t)D * DV + threadIdx.x] = nj;
+    if (threadIdx.x == blockDim.x - 1) st[(size_t)D * DV + D] = m;
+  }
 }
 
-static size_t mlstm_smem_bytes(int D, int DV) {
-  const int P = scan_parts(D > DV ? D : DV);
-  const size_t state = scan_rows(D, D > DV ? D : DV) ? 0 : (size_t)((D * DV + 3) & ~3);
-  return (state + (size_t)SCAN_CT * (3 * D + (2 + P) * DV + 4) + 64 * 2) * sizeof(float);
+static size_t mlstm_smem_bytes(int D, int CW, int P, int R) {
+  const size_t state = R ? 0 : (size_t)((D * CW + 3) & ~3);
+  return (state + (size_t)SCAN_CT * (3 * D + (2 + P) * CW + 4) + 64 * 2) * sizeof(float);
 }
 
 MB_EXPORT int mb_mlstm_scan(const float* z, int ld, int cq, int ck, int cv, int cg, int ci, int cf,
                             const float* bi, const float* bf, float cap, float q_scale,
                             const float* normw, float eps, float* state, long long state_stride,
                             long long state_off, const int* seq_start, const int* seq_slot,
-                            void* out, int dtype, int B, int H, int D, int DV, void* stream) {
+                            void* out, float* raw, int dtype, int T_, int B, int H, int D, int DV,
+                            void* stream) {
   if (B <= 0) return 0;
-  const size_t smem = mlstm_smem_bytes(D, DV);
-  if (D <= 0 || DV <= 0 || D > 512 || DV > 512 || smem > 200 * 1024)
-    MB_FAIL("mb_mlstm_scan: heads of %d x %d values (at most 512 each, and what a block stages "
-            "must fit 200 KB)", D, DV);
+  if (D <= 0 || DV <= 0 || D > 512 || DV > 512)
+    MB_FAIL("mb_mlstm_scan: heads of %d x %d values (at most 512 each)", D, DV);
+  const int NS = raw ? scan_slices(B, H, D, DV, D) : 1;
+  const int CW = (DV + NS - 1) / NS;
+  // one slice: a block as wide as the larger of D and DV; several: as wide as the slice
+  const int width = NS == 1 ? (D > DV ? D : DV) : CW;
+  const int P = scan_parts(width), per = (D + P - 1) / P;
+  const int R = per <= 8 ? 8 : per <= 16 ? 16 : per <= 32 ? 32 : 0;
+  const size_t smem = mlstm_smem_bytes(D, CW, P, R);
+  if (smem > 200 * 1024)
+    MB_FAIL("mb_mlstm_scan: heads of %d x %d values (what a block stages must fit 200 KB)", D, DV);
   cudaStream_t s = (cudaStream_t)stream;
-  const int threads = ((D > DV ? D : DV) + 31) / 32 * 32 * scan_parts(D > DV ? D : DV);
-#define GO(T_, R_)                                                                             \
+  const int threads = (width + 31) / 32 * 32 * P;
+  float* raw_used = NS > 1 ? raw : nullptr;
+#define GO(T_t, R_)                                                                            \
   {                                                                                            \
     static size_t configured = 48 * 1024;                                                      \
     if (smem > configured) {                                                                   \
-      cudaFuncSetAttribute(mlstm_scan_kernel<T_, R_>,                                          \
+      cudaFuncSetAttribute(mlstm_scan_kernel<T_t, R_>,                                         \
                            cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);           \
       configured = 200 * 1024;                                                                 \
     }                                                                                          \
-    mb_launch(mlstm_scan_kernel<T_, R_>, dim3(B, H), dim3(threads), smem, s, z, ld, cq, ck, cv, \
-              cg, ci, cf, bi, bf, cap, q_scale, normw, eps, state, (size_t)state_stride,       \
-              (size_t)state_off, seq_start, seq_slot, (T_*)out, H, D, DV);                     \
+    mb_launch(mlstm_scan_kernel<T_t, R_>, dim3(B, H, NS), dim3(threads), smem, s, z, ld, cq,   \
+              ck, cv, cg, ci, cf, bi, bf, cap, q_scale, normw, eps, state,                     \
+              (size_t)state_stride, (size_t)state_off, seq_start, seq_slot, (T_t*)out,         \
+              raw_used, H, D, DV);                                                             \
+    if (NS > 1) launch_head_norm<T_t>(raw, z + cg, ld, normw, eps, 1, out, T_, H, DV, s);      \
   }
-#define GOR(T_)                                                                                \
-  switch (scan_rows(D, D > DV ? D : DV)) {                                                     \
-    case 8: GO(T_, 8) break;                                                                   \
-    case 16: GO(T_, 16) break;                                                                 \
-    case 32: GO(T_, 32) break;                                                                 \
-    case 64: GO(T_, 64) break;                                                                 \
-    default: GO(T_, 0)                                                                         \
+#define GOR(T_t)                                                                               \
+  switch (R) {                                                                                 \
+    case 8: GO(T_t, 8) break;                                                                  \
+    case 16: GO(T_t, 16) break;                                                                \
+    case 32: GO(T_t, 32) break;                                                                \
+    default: GO(T_t, 0)                                                                        \
   }
   if (dtype == MB_F32) GOR(float) else GOR(__nv_bfloat16)
 #undef GOR

@@ -412,13 +412,16 @@ def wkv_scan(r, k, v, lw, g, w0, u, normw, eps: float, state: torch.Tensor,
     _contig(out, "out"), _contig(h, "h")
     assert out.dtype == h.dtype and out.shape == (T, heads * dim) and state.dtype == torch.float32
     assert state.stride(1) == 1 and state.shape[1] >= h.shape[1] + heads * dim * dim
+    # where a step has few (sequence, head) pairs a head's columns are dealt over several
+    # blocks, which leave their outputs here for the kernel that norms and gates them
+    raw = torch.empty((T, heads * dim), dtype=torch.float32, device=out.device)
     _call("recurrent", "mb_wkv_scan",
           [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _f, _vp, _ll, _ll, _vp, _i, _i, _vp, _vp,
-           _vp, _i, _i, _i, _vp],
+           _vp, _vp, _i, _i, _i, _i, _vp],
           _ptr(r), _ptr(k), _ptr(v), _ptr(lw), _ptr(g), ld, _ptr(w0), _ptr(u), _ptr(normw),
           float(eps), _ptr(state), state.stride(0), state_off, _ptr(h), code_of(h.dtype),
-          h.shape[1], _ptr(step.seq_start), _ptr(step.seq_slot), _ptr(out), step.B, heads, dim,
-          _stream())
+          h.shape[1], _ptr(step.seq_start), _ptr(step.seq_slot), _ptr(out), _ptr(raw), T, step.B,
+          heads, dim, _stream(), launches=1 if step.B * heads >= 96 else 2)
 
 
 def mlstm_scan(z: torch.Tensor, cols, bi, bf, cap: float, q_scale: float, normw, eps: float,
@@ -437,13 +440,14 @@ def mlstm_scan(z: torch.Tensor, cols, bi, bf, cap: float, q_scale: float, normw,
     _contig(out, "out")
     assert out.shape == (T, heads * vdim) and state.dtype == torch.float32
     assert state.stride(1) == 1 and state.shape[1] >= heads * (dim * vdim + dim + 1)
+    raw = torch.empty((T, heads * vdim), dtype=torch.float32, device=out.device)   # as in wkv_scan
     _call("recurrent", "mb_mlstm_scan",
           [_vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _f, _vp, _f, _vp, _ll, _ll, _vp, _vp,
-           _vp, _i, _i, _i, _i, _i, _vp],
+           _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
           _ptr(z), z.stride(0), *[int(c) for c in cols], _ptr(bi), _ptr(bf), float(cap),
           float(q_scale), _ptr(normw), float(eps), _ptr(state), state.stride(0), state_off,
-          _ptr(step.seq_start), _ptr(step.seq_slot), _ptr(out), code_of(out.dtype), step.B,
-          heads, dim, vdim, _stream())
+          _ptr(step.seq_start), _ptr(step.seq_slot), _ptr(out), _ptr(raw), code_of(out.dtype), T,
+          step.B, heads, dim, vdim, _stream(), launches=1 if step.B * heads >= 96 else 2)
 
 
 # ------------------------------------------------------------------------------ latent attention

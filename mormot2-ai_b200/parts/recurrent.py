@@ -37,12 +37,12 @@ def _scan_parts(columns: int) -> int:
 
 def _scan_smem(dim: int, vdim: int, staged_per_token: int) -> int:
     """Bytes of shared memory of a scan kernel's block: sixteen staged tokens, and the state
-    unless a thread's share of a column (at most 64 rows) lies in registers."""
+    unless a thread's share of a column (at most 32 rows) lies in registers."""
     columns = max(dim, vdim)
     if columns > 512:
         return 1 << 30
     rows = -(-dim // _scan_parts(columns))
-    state = 0 if rows <= 64 else dim * vdim + 4
+    state = 0 if rows <= 32 else dim * vdim + 4
     return 4 * (state + 16 * staged_per_token + 256)
 
 

@@ -202,7 +202,7 @@ def test_streams_kernel(dtype, S, H):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,dim,hidden", [(3, 12, 40), (2, 64, 96), (1, 33, 50)])
+@pytest.mark.parametrize("heads,dim,hidden", [(3, 12, 40), (2, 64, 96), (1, 33, 50), (1, 160, 64)])
 def test_decaying_state_mixer_alone(dtype, heads, dim, hidden):
     """Whole sequences, then the same in portions of 1, 2 and 30 tokens with a batch mate:
     the state and the last row carry over; slots' states do not mix."""
@@ -229,8 +229,12 @@ def test_decaying_state_mixer_alone(dtype, heads, dim, hidden):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,dim,vdim,hidden", [(3, 20, 12, 40), (2, 32, 64, 96), (1, 9, 22, 50)])
+@pytest.mark.parametrize("heads,dim,vdim,hidden", [(3, 20, 12, 40), (2, 32, 64, 96), (1, 9, 22, 50),
+                                                    (2, 128, 128, 64), (1, 40, 200, 48)])
 def test_matrix_memory_mixer_alone(dtype, heads, dim, vdim, hidden):
+    """The last two sizes have heads so large that a head's columns are dealt over several
+    blocks and normed by a kernel after (few sequences and heads); (1, 40, 200) with slices
+    that do not divide evenly."""
     rt = Runtime(TORCH[dtype])
     p = {"heads": heads, "dim": dim, "vdim": vdim, "gate_cap": 6.0}
     names = {s: s for s in ("q", "k", "v", "g", "o", "norm", "i", "f")}
