@@ -24,7 +24,17 @@ struct StTerms {
   int n;
 };
 
-template <typename TW, typename TO>
+__device__ __forceinline__ float4 f4_scale(float a, float4 v) {
+  return make_float4(a * v.x, a * v.y, a * v.z, a * v.w);
+}
+__device__ __forceinline__ float4 f4_fma(float a, float4 v, float4 acc) {
+  return make_float4(fmaf(a, v.x, acc.x), fmaf(a, v.y, acc.y), fmaf(a, v.z, acc.z),
+                     fmaf(a, v.w, acc.w));
+}
+
+// V = 4: four neighbouring columns a thread and step (H a multiple of 4, every pointer on a
+// 16-byte boundary); V = 1: one. The arithmetic of a column is the same in both.
+template <typename TW, typename TO, int V>
 __global__ void stream_step_kernel(float* __restrict__ x, size_t stream_stride, int S,
                                    const float* __restrict__ mix, const float* __restrict__ outc,
                                    StTerms terms, const float* __restrict__ in,
@@ -32,7 +42,7 @@ __global__ void stream_step_kernel(float* __restrict__ x, size_t stream_stride, 
                                    const int* __restrict__ rows, int H) {
   mb_grid_wait();
   mb_grid_launch_next();
-  extern __shared__ float st_smem[];  // H values of u, then 33 for the reductions
+  extern __shared__ __align__(16) float st_smem[];  // H values of u, then 33 for the reductions
   __shared__ float s_mix[ST_MAX_STREAMS * ST_MAX_STREAMS], s_out[ST_MAX_STREAMS],
       s_in[ST_MAX_STREAMS];
   float* u_row = st_smem;
@@ -46,39 +56,79 @@ __global__ void stream_step_kernel(float* __restrict__ x, size_t stream_stride, 
   }
   __syncthreads();
   float sum = 0.f;
-  for (int c = threadIdx.x; c < H; c += blockDim.x) {
-    float xs[ST_MAX_STREAMS];
-#pragma unroll
-    for (int s = 0; s < ST_MAX_STREAMS; ++s)
-      xs[s] = s < S ? x[(size_t)s * stream_stride + (size_t)t * H + c] : 0.f;
-    if (mix) {
-      float y = 0.f;
-      for (int b = 0; b < terms.n; ++b) {
-        const float v = terms.y[b][(size_t)t * H + c];
-        y = b == 0 ? terms.scale[0] * v : fmaf(terms.scale[b], v, y);
-      }
-      float nx[ST_MAX_STREAMS];
-#pragma unroll
-      for (int to = 0; to < ST_MAX_STREAMS; ++to) {
-        if (to < S) {
-          float v = s_out[to] * y;
-#pragma unroll
-          for (int s = 0; s < ST_MAX_STREAMS; ++s)
-            if (s < S) v = fmaf(s_mix[s * S + to], xs[s], v);
-          nx[to] = v;
-          x[(size_t)to * stream_stride + (size_t)t * H + c] = v;
-        }
-      }
-#pragma unroll
-      for (int s = 0; s < ST_MAX_STREAMS; ++s) xs[s] = s < S ? nx[s] : 0.f;
-    }
-    if (w) {
-      float u = 0.f;
+  if (V == 4) {
+    for (int c = 4 * threadIdx.x; c < H; c += 4 * blockDim.x) {
+      float4 xs[ST_MAX_STREAMS];
 #pragma unroll
       for (int s = 0; s < ST_MAX_STREAMS; ++s)
-        if (s < S) u = s == 0 ? s_in[0] * xs[0] : fmaf(s_in[s], xs[s], u);
-      u_row[c] = u;
-      sum += u;
+        xs[s] = s < S ? *(const float4*)(x + (size_t)s * stream_stride + (size_t)t * H + c)
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
+      if (mix) {
+        float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int b = 0; b < terms.n; ++b) {
+          const float4 v = *(const float4*)(terms.y[b] + (size_t)t * H + c);
+          y = b == 0 ? f4_scale(terms.scale[0], v) : f4_fma(terms.scale[b], v, y);
+        }
+        float4 nx[ST_MAX_STREAMS];
+#pragma unroll
+        for (int to = 0; to < ST_MAX_STREAMS; ++to) {
+          if (to < S) {
+            float4 v = f4_scale(s_out[to], y);
+#pragma unroll
+            for (int s = 0; s < ST_MAX_STREAMS; ++s)
+              if (s < S) v = f4_fma(s_mix[s * S + to], xs[s], v);
+            nx[to] = v;
+            *(float4*)(x + (size_t)to * stream_stride + (size_t)t * H + c) = v;
+          }
+        }
+#pragma unroll
+        for (int s = 0; s < ST_MAX_STREAMS; ++s)
+          if (s < S) xs[s] = nx[s];
+      }
+      if (w) {
+        float4 u = f4_scale(s_in[0], xs[0]);
+#pragma unroll
+        for (int s = 1; s < ST_MAX_STREAMS; ++s)
+          if (s < S) u = f4_fma(s_in[s], xs[s], u);
+        *(float4*)(u_row + c) = u;
+        sum += (u.x + u.y) + (u.z + u.w);
+      }
+    }
+  } else {
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+      float xs[ST_MAX_STREAMS];
+#pragma unroll
+      for (int s = 0; s < ST_MAX_STREAMS; ++s)
+        xs[s] = s < S ? x[(size_t)s * stream_stride + (size_t)t * H + c] : 0.f;
+      if (mix) {
+        float y = 0.f;
+        for (int b = 0; b < terms.n; ++b) {
+          const float v = terms.y[b][(size_t)t * H + c];
+          y = b == 0 ? terms.scale[0] * v : fmaf(terms.scale[b], v, y);
+        }
+        float nx[ST_MAX_STREAMS];
+#pragma unroll
+        for (int to = 0; to < ST_MAX_STREAMS; ++to) {
+          if (to < S) {
+            float v = s_out[to] * y;
+#pragma unroll
+            for (int s = 0; s < ST_MAX_STREAMS; ++s)
+              if (s < S) v = fmaf(s_mix[s * S + to], xs[s], v);
+            nx[to] = v;
+            x[(size_t)to * stream_stride + (size_t)t * H + c] = v;
+          }
+        }
+#pragma unroll
+        for (int s = 0; s < ST_MAX_STREAMS; ++s) xs[s] = s < S ? nx[s] : 0.f;
+      }
+      if (w) {
+        float u = 0.f;
+#pragma unroll
+        for (int s = 0; s < ST_MAX_STREAMS; ++s)
+          if (s < S) u = s == 0 ? s_in[0] * xs[0] : fmaf(s_in[s], xs[s], u);
+        u_row[c] = u;
+        sum += u;
+      }
     }
   }
   if (!w) return;
@@ -89,8 +139,17 @@ __global__ void stream_step_kernel(float* __restrict__ x, size_t stream_stride, 
     dev = fmaf(d, d, dev);
   }
   const float inv = 1.0f / sqrtf(block_sum(dev, red) / (float)H + eps);
-  for (int c = threadIdx.x; c < H; c += blockDim.x)
-    out[(size_t)r * H + c] = from_f32<TO>((u_row[c] - mean) * inv * to_f32<TW>(w[c]));
+  if (V == 4) {
+    for (int c = 4 * threadIdx.x; c < H; c += 4 * blockDim.x) {
+      const float4 u = *(const float4*)(u_row + c), ww = load4<TW>(w + c);
+      store4<TO>(out + (size_t)r * H + c,
+                 make_float4((u.x - mean) * inv * ww.x, (u.y - mean) * inv * ww.y,
+                             (u.z - mean) * inv * ww.z, (u.w - mean) * inv * ww.w));
+    }
+  } else {
+    for (int c = threadIdx.x; c < H; c += blockDim.x)
+      out[(size_t)r * H + c] = from_f32<TO>((u_row[c] - mean) * inv * to_f32<TW>(w[c]));
+  }
 }
 
 // x: [S][T, H] float32, stream s at x + s * stream_stride. mix [S, S], outc [S] and the terms:
@@ -117,24 +176,31 @@ MB_EXPORT int mb_stream_step(float* x, long long stream_stride, int S, const flo
   const size_t smem = ((size_t)H + 33) * sizeof(float);
   if (smem > 200 * 1024) MB_FAIL("mb_stream_step: rows of %d values", H);
   cudaStream_t s = (cudaStream_t)stream;
-  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-#define GO(TW_, TO_)                                                                          \
+  // four columns a thread where everything lies on 16-byte boundaries
+  uintptr_t bits = (uintptr_t)x | (uintptr_t)w | (uintptr_t)out | (uintptr_t)(stream_stride * 4);
+  for (int b = 0; b < terms.n; ++b) bits |= (uintptr_t)terms.y[b];
+  const bool vec = H % 4 == 0 && (bits & 15) == 0;
+  const int per = vec ? 4 : 1;
+  const int threads = H >= 2048 * per ? 512 : (H >= 512 * per ? 256 : 128);
+#define GOV(TW_, TO_, V_)                                                                     \
   {                                                                                           \
     static size_t configured = 48 * 1024;                                                     \
     if (smem > configured) {                                                                  \
-      cudaFuncSetAttribute(stream_step_kernel<TW_, TO_>,                                      \
+      cudaFuncSetAttribute(stream_step_kernel<TW_, TO_, V_>,                                  \
                            cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);          \
       configured = 200 * 1024;                                                                \
     }                                                                                         \
-    mb_launch(stream_step_kernel<TW_, TO_>, dim3(R), dim3(threads), smem, s, x,               \
+    mb_launch(stream_step_kernel<TW_, TO_, V_>, dim3(R), dim3(threads), smem, s, x,           \
               (size_t)stream_stride, S, mix, outc, terms, in, (const TW_*)w, eps, (TO_*)out,  \
               rows, H);                                                                       \
   }
+#define GO(TW_, TO_) { if (vec) GOV(TW_, TO_, 4) else GOV(TW_, TO_, 1) }
   if (w_dtype == MB_F32 && out_dtype == MB_F32) GO(float, float)
   else if (w_dtype == MB_F32) GO(float, __nv_bfloat16)
   else if (out_dtype == MB_F32) GO(__nv_bfloat16, float)
   else GO(__nv_bfloat16, __nv_bfloat16)
 #undef GO
+#undef GOV
   MB_CHECK_LAUNCH("mb_stream_step");
 }
 
