@@ -16,7 +16,7 @@
 MB_DEFINE_LAST_ERROR
 
 #define ST_MAX_STREAMS 8
-#define ST_MAX_TERMS 4
+#define ST_MAX_TERMS 16
 
 struct StTerms {
   const float* y[ST_MAX_TERMS];  // [T, H] float32 each

@@ -75,7 +75,7 @@ CLASS_OF = {"mb_gemm_tc": "products", "mb_gemm_simt": "products",
             "mb_moe_route": "routing", "mb_moe_plan": "routing", "mb_moe_route_plan": "routing", "mb_moe_gemm": "products",
             "mb_moe_combine": "routing", "mb_stream_step": "norms", "mb_add_scaled": "norms",
             "mb_token_shift": "recurrence", "mb_wkv_scan": "recurrence",
-            "mb_mlstm_scan": "recurrence"}
+            "mb_mlstm_scan": "recurrence", "mb_tanh": "recurrence"}
 
 
 class Timing:

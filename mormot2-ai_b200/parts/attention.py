@@ -99,7 +99,7 @@ class GqaAttention(Part):
     def forward(self, h, x, step, line, state, writes_cache: bool, store: bool = False):
         """Adds the mixer's output into x, or returns it as ``Pending`` split sums for the next
         norm to add (a decode step whose output product splits K). ``store``: x receives the
-        output instead (nothing is left pending then)."""
+        output instead of a sum onto it, or the split sums are returned and x is left as it is."""
         from .linear import Pending
         T = h.shape[0]
         nkv = self.nkv if writes_cache else 0
@@ -140,9 +140,9 @@ class GqaAttention(Part):
 
     def _project(self, attn, x, store: bool):
         from .linear import Pending
-        if store:
-            self.o(attn, out=x)
-            return None
+        if store:       # stored into x, or left pending (x is then not touched)
+            out = self.o(attn, out=x, defer=True)
+            return out if isinstance(out, Pending) else None
         out = self.o(attn, add_into=x, defer=True)
         return out if isinstance(out, Pending) else None
 

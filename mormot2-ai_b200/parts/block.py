@@ -133,9 +133,15 @@ class HyperConnectionsBlock(Part):
         y = torch.empty((h.shape[0], h.shape[1]), dtype=torch.float32, device=h.device)
         if getattr(part, "can_store", False):
             pending = part.forward(h, y, *args, store=True)
-        else:
-            y.zero_()
-            pending = part.forward(h, y, *args)
+            if pending is not None and len(pending.partial) <= 16:
+                # the sublayer left its output as split sums: each is a term of the write-back
+                return [(part_sum, 1.0) for part_sum in pending.partial]
+            if pending is not None:      # more terms than the kernel takes: summed here
+                y.zero_()
+                settle(y, pending)
+            return [(y, 1.0)]
+        y.zero_()
+        pending = part.forward(h, y, *args)
         if pending is not None:
             settle(y, pending)
         return [(y, 1.0)]

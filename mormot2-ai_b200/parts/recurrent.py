@@ -27,7 +27,7 @@ import torch
 from .. import kernels as K
 from ..errors import ConfigError
 from .base import MIXERS, Part, StateNeed, TensorNeed
-from .linear import Linear
+from .linear import Linear, Pending
 
 
 def _scan_parts(columns: int) -> int:
@@ -44,6 +44,17 @@ def _scan_smem(dim: int, vdim: int, staged_per_token: int) -> int:
     rows = -(-dim // _scan_parts(columns))
     state = 0 if rows <= 32 else dim * vdim + 4
     return 4 * (state + 16 * staged_per_token + 256)
+
+
+def _project(linear: Linear, y, x, store: bool):
+    """The output product: added into x, or (``store``) written into x, or, where the product
+    of a step of few tokens splits its sums, left as ``Pending`` for whoever reads it next (x is
+    then not touched)."""
+    if store:
+        out = linear(y, out=x, defer=True)
+        return out if isinstance(out, Pending) else None
+    linear(y, add_into=x)
+    return None
 
 
 def _f32(t: torch.Tensor) -> torch.Tensor:
@@ -116,11 +127,7 @@ class WkvMixer(Part):
         K.wkv_scan(z[:, :HD], z[:, HD:2 * HD], z[:, 2 * HD:3 * HD], z[:, 4 * HD + R:],
                    z[:, 3 * HD:4 * HD], self.w0, self.u, self.norm, self.eps, state, h, step, y,
                    self.nh, self.dim)
-        if store:
-            self.o(y, out=x)
-        else:
-            self.o(y, add_into=x)
-        return None
+        return _project(self.o, y, x, store)
 
 
 class MlstmMixer(Part):
@@ -177,11 +184,7 @@ class MlstmMixer(Part):
         y = torch.empty((T, self.nh * self.vdim), dtype=self.rt.dtype, device=h.device)
         K.mlstm_scan(z, self.cols, self.bi, self.bf, self.cap, self.dim ** -0.5, self.norm,
                      self.eps, state, step, y, self.nh, self.dim, self.vdim)
-        if store:
-            self.o(y, out=x)
-        else:
-            self.o(y, add_into=x)
-        return None
+        return _project(self.o, y, x, store)
 
 
 MIXERS.register("wkv", WkvMixer)

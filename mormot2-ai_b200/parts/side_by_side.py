@@ -70,18 +70,28 @@ class SideBySide(Part):
     def forward_branches(self, h, step, line, state, writes_cache: bool):
         """Runs every branch and returns ``[(y_b float32 [T, hidden], factor_b)]``: whoever
         adds the outputs into the residual does the weighted sum on the way."""
-        terms = []
+        terms, terms_of = [], []
         for b, scale, (at, n) in zip(self.branches, self.scales, self.offsets):
+            terms_of.append(b)
             y = torch.empty((h.shape[0], h.shape[1]), dtype=torch.float32, device=h.device)
             sub_state = state[:, at:at + n] if n else None
             sub_line = line if b.cache_need() is not None else None
             if getattr(b, "can_store", False):
                 pending = b.forward(h, y, step, sub_line, sub_state, writes_cache, store=True)
+                # a later branch may need a term for a buffer of its own
+                left = len(self.branches) - len(terms_of)
+                if pending is not None and len(terms) + len(pending.partial) + left <= 16:
+                    # the branch left its output as split sums: each is a term of its own
+                    terms += [(part, scale) for part in pending.partial]
+                    continue
+                if pending is not None:      # more terms than a kernel takes: summed here
+                    y.zero_()
+                    K.add_partials(y, pending.partial)
             else:
                 y.zero_()
                 pending = b.forward(h, y, step, sub_line, sub_state, writes_cache)
-            if pending is not None:
-                K.add_partials(y, pending.partial)
+                if pending is not None:
+                    K.add_partials(y, pending.partial)
             terms.append((y, scale))
         return terms
 
