@@ -622,6 +622,14 @@ def test_other_orders_of_layers(tmp_path):
         eng.close(slot)
         check(np.concatenate(got), ref, "float32", f"order {k}")
         eng.rt.check()
+        # and through the entry point's scheduler (with no page pool to count in model 0)
+        client = LlmClient(folder, dtype="float32", max_batch=2, cache_tokens=256)
+        prompts = [ids[:5], ids[5:40], ids[40:42]]
+        for p, tokens in zip(prompts, client.generate(prompts, max_tokens=3, temperature=0.0, stop=[])):
+            seq = list(p)
+            for a in tokens:
+                assert a == int(np.argmax(plain.forward(cfg, W, seq)[-1])), (k, seq, a)
+                seq.append(a)
 
 
 def test_a_step_that_fails_leaves_the_state_as_it_found_it(small_u):
